@@ -1,0 +1,5 @@
+"""Alias of ``mdy_triton_b200.core.triton_maxmin`` under the reference's import path."""
+import importlib as _importlib
+
+_impl = _importlib.import_module("mdy_triton_b200.core.triton_maxmin")
+globals().update({k: v for k, v in vars(_impl).items() if not k.startswith("__")})

@@ -1,0 +1,464 @@
+"""GPU parity tests: the CUDA kernels, reached through the operator API (which calls the C-ABI), against
+(1) the golden vectors the reference's own kernels produced and (2) the float32 CPU oracle, on seeded
+inputs.  Tolerances: conftest.REL (1e-2 relative for 16-bit I/O, 1e-4 for float32 I/O) and 1e-4 on the
+float32 loss."""
+import pytest
+import torch
+
+from conftest import LOSS_TOL, REL, assert_close, golden_cases
+from oracle import eager as E
+import mdy_triton.core as core
+from mdy_triton.core.cross_entyopy_loss import _FastCrossEntropyLoss, triton_entropy_loss
+from mdy_triton_b200 import _C
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def g(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def leaf(t):
+    return t.detach().to(DEV).clone().requires_grad_(True)
+
+
+def loss_close(a, b):
+    a, b = float(a), float(b)
+    assert abs(a - b) <= LOSS_TOL * max(1.0, abs(b)), (a, b)
+
+
+# ---------------------------------------------------------------------------------------------- RMSNorm
+def run_rmsnorm(x, w, eps, dy):
+    xg, wg = leaf(x), leaf(w)
+    y = core.triton_rmsnorm(xg, wg, eps)
+    y.backward(dy.to(DEV))
+    return y, xg.grad, wg.grad
+
+
+@pytest.mark.parametrize("c", golden_cases("rmsnorm.pt"))
+def test_rmsnorm_golden(c):
+    y, dx, dw = run_rmsnorm(c["x"], c["w"], c["eps"], c["dy"])
+    r = REL[c["x"].dtype]
+    assert y.dtype == c["x"].dtype and dw.dtype == c["w"].dtype
+    assert_close(y, c["y"], r, "y"); assert_close(dx, c["dx"], r, "dx"); assert_close(dw, c["dw"], r, "dw")
+
+
+@pytest.mark.parametrize("m,n,dt", [(4096, 896, torch.bfloat16), (4096, 896, torch.float32), (2048, 3584, torch.bfloat16),
+                                    (1024, 2048, torch.float16), (1, 4096, torch.bfloat16), (3, 8, torch.float32),
+                                    (5, 1, torch.float32), (7, 7, torch.bfloat16), (9, 127, torch.float16),
+                                    (9, 129, torch.bfloat16), (64, 3585, torch.bfloat16), (300, 8192, torch.bfloat16),
+                                    (40, 16384, torch.bfloat16), (12, 32768, torch.bfloat16), (6, 65536, torch.bfloat16),
+                                    (4, 70000, torch.float32), (33, 5120, torch.float32)])
+def test_rmsnorm_vs_oracle(m, n, dt):
+    gen = g(m * 131 + n)
+    x = torch.randn(m, n, generator=gen).to(dt); w = (1 + 0.02 * torch.randn(n, generator=gen)).to(dt)
+    dy = torch.randn(m, n, generator=gen).to(dt)
+    y, dx, dw = run_rmsnorm(x, w, 1e-6, dy)
+    yo, _ = E.rmsnorm_fwd(x, w, 1e-6)
+    dxo, dwo = E.rmsnorm_bwd(dy, x, w, 1e-6)
+    r = REL[dt]
+    assert_close(y, yo, r, "y"); assert_close(dx, dxo, r, "dx")
+    assert_close(dw, dwo, max(r, 2e-3) if dt == torch.float32 else r, "dw")
+
+
+def test_rmsnorm_3d_input_strided_rows_and_fp32_weight():
+    gen = g(5)
+    big = torch.randn(2, 6, 512 + 64, generator=gen).to(torch.bfloat16).to(DEV)
+    x = big[..., :512]  # row stride 576: not contiguous, still 16-byte aligned rows
+    w = (1 + 0.1 * torch.randn(512, generator=gen)).to(DEV)  # float32 master weight
+    xg = x.detach().clone().requires_grad_(True)
+    xs = big.detach().clone()[..., :512].requires_grad_(True)
+    wg1, wg2 = leaf(w), leaf(w)
+    dy = torch.randn(2, 6, 512, generator=gen).to(torch.bfloat16).to(DEV)
+    y1 = core.triton_rmsnorm(xg, wg1, 1e-5); y1.backward(dy)
+    y2 = core.triton_rmsnorm(xs, wg2, 1e-5); y2.backward(dy)
+    assert y1.shape == (2, 6, 512) and wg1.grad.dtype == torch.float32
+    assert torch.equal(y1, y2) and torch.equal(wg1.grad, wg2.grad)
+    yo, _ = E.rmsnorm_fwd(x.cpu(), w.cpu(), 1e-5)
+    dxo, dwo = E.rmsnorm_bwd(dy.cpu(), x.cpu(), w.cpu(), 1e-5)
+    assert_close(y1, yo, 1e-2); assert_close(xg.grad, dxo, 1e-2); assert_close(wg1.grad, dwo, 1e-2)
+
+
+def test_rmsnorm_unaligned_base_takes_scalar_path():
+    gen = g(6)
+    flat = torch.randn(16 * 64 + 1, generator=gen).to(torch.bfloat16).to(DEV)
+    x = flat[1:].view(16, 64)  # base pointer off by 2 bytes
+    w = torch.ones(64, dtype=torch.bfloat16, device=DEV)
+    y = core.triton_rmsnorm(x, w, 1e-6)
+    assert_close(y, E.rmsnorm_fwd(x.cpu(), w.cpu(), 1e-6)[0], 1e-2)
+
+
+def test_rmsnorm_scale_invariance_full_size():
+    """Size-independent property at the Qwen2-7B shape: rmsnorm(4x) == rmsnorm(x) up to eps."""
+    x = torch.randn(32768, 3584, device=DEV, dtype=torch.bfloat16, generator=torch.Generator(DEV).manual_seed(2))
+    w = torch.ones(3584, device=DEV, dtype=torch.bfloat16)
+    y1 = core.triton_rmsnorm(x, w, 1e-6)
+    y4 = core.triton_rmsnorm(x * 4, w, 1e-6)
+    assert (y1.float() - y4.float()).abs().max() <= 0.04
+    ms = y1.float().pow(2).mean(-1)
+    assert (ms - 1).abs().max() < 2e-2
+
+
+# ------------------------------------------------------------------------------------------ add+RMSNorm
+def run_add_rmsnorm(x, res, w, eps, dy, dn):
+    xg, rg, wg = leaf(x), leaf(res), leaf(w)
+    y, nr = core.triton_fused_add_norm(xg, rg, wg, eps)
+    torch.autograd.backward([y, nr], [dy.to(DEV), dn.to(DEV)])
+    return y, nr, xg.grad, rg.grad, wg.grad
+
+
+@pytest.mark.parametrize("c", golden_cases("add_rmsnorm.pt"))
+def test_add_rmsnorm_golden(c):
+    y, nr, dx, dr, dw = run_add_rmsnorm(c["x"], c["res"], c["w"], c["eps"], c["dy"], c["dnew_res"])
+    r = REL[c["x"].dtype]
+    assert_close(y, c["y"], r, "y"); assert_close(nr, c["new_res"], r, "new_res")
+    if c["grads"]:
+        assert_close(dx, c["dx"], r, "dx"); assert_close(dr, c["dres"], r, "dres")
+        dw_ref = c["dw"].float().sum(0) if c["dw"].dim() == 2 else c["dw"]
+        assert_close(dw, dw_ref, r, "dw")
+
+
+@pytest.mark.parametrize("m,n,dt,eps", [(2048, 4096, torch.bfloat16, 1e-5), (4096, 896, torch.float32, 1e-6),
+                                        (512, 2048, torch.float16, 1e-5), (1, 256, torch.bfloat16, 1e-5),
+                                        (17, 129, torch.float32, 1e-6), (5, 3585, torch.bfloat16, 1e-6),
+                                        (64, 8192, torch.bfloat16, 1e-5), (8, 20480, torch.bfloat16, 1e-5)])
+def test_add_rmsnorm_vs_oracle(m, n, dt, eps):
+    """Includes hidden sizes > 128, where the reference backward is wrong: checked against the oracle
+    (closed form == autograd of `residual + x` followed by RMSNorm)."""
+    gen = g(m * 7 + n)
+    x = torch.randn(m, n, generator=gen).to(dt); res = torch.randn(m, n, generator=gen).to(dt)
+    w = (1 + 0.02 * torch.randn(n, generator=gen)).to(dt)
+    dy = torch.randn(m, n, generator=gen).to(dt); dn = torch.randn(m, n, generator=gen).to(dt)
+    y, nr, dx, dr, dw = run_add_rmsnorm(x, res, w, eps, dy, dn)
+    yo, so, _ = E.add_rmsnorm_fwd(x, res, w, eps)
+    r = REL[dt]
+    assert_close(y, yo, r, "y"); assert_close(nr, so, r, "new_res")
+    # backward consumes the ROUNDED new residual the forward stored
+    dxo, dwo = E.add_rmsnorm_bwd(dy, dn, nr.cpu(), w, eps)
+    assert_close(dx, dxo, r, "dx"); assert torch.equal(dx, dr)
+    assert_close(dw, dwo, max(r, 2e-3), "dw")
+
+
+def test_add_rmsnorm_unused_outputs():
+    x = torch.randn(8, 256, device=DEV, dtype=torch.bfloat16)
+    w = torch.ones(256, device=DEV, dtype=torch.bfloat16)
+    xg, rg, wg = leaf(x), leaf(x), leaf(w)
+    y, nr = core.triton_fused_add_norm(xg, rg, wg, 1e-5)
+    y.float().sum().backward()           # new_residual unused -> its gradient is None
+    dxo, _ = E.add_rmsnorm_bwd(torch.ones(8, 256), None, nr.cpu(), w.cpu(), 1e-5)
+    assert_close(xg.grad, dxo, 1e-2)
+    xg, rg, wg = leaf(x), leaf(x), leaf(w)
+    y, nr = core.triton_fused_add_norm(xg, rg, wg, 1e-5)
+    nr.float().sum().backward()          # y unused
+    assert torch.equal(xg.grad, torch.ones_like(xg)) and torch.equal(wg.grad, torch.zeros_like(wg))
+
+
+# ------------------------------------------------------------------------------------------------- RoPE
+def run_rope(c_q, c_k, cos, sin, dq, dk, strided_grad=False):
+    # storage layout [B, L, H, D], logical [B, H, L, D] — what q_proj(...).view().transpose(1, 2) yields
+    qs = leaf(c_q.transpose(1, 2).contiguous()); ks = leaf(c_k.transpose(1, 2).contiguous())
+    q_in = (qs * 1.0).transpose(1, 2); k_in = (ks * 1.0).transpose(1, 2)
+    qe, ke = core.fused_apply_rope(q_in, k_in, cos.to(DEV), sin.to(DEV))
+    assert qe.data_ptr() == q_in.data_ptr() and ke.data_ptr() == k_in.data_ptr()  # in place
+    dq, dk = dq.to(DEV), dk.to(DEV)
+    if strided_grad:  # gradient arriving in [B, H, L, D] storage, like an attention backward's
+        dq, dk = dq.contiguous(), dk.contiguous()
+    qv, kv = qe.detach().clone(), ke.detach().clone()
+    torch.autograd.backward([qe, ke], [dq, dk])
+    return qv, kv, qs.grad.transpose(1, 2), ks.grad.transpose(1, 2)
+
+
+@pytest.mark.parametrize("c", golden_cases("rope.pt"))
+def test_rope_golden(c):
+    qe, ke, gq, gk = run_rope(c["q"], c["k"], c["cos"], c["sin"], c["dq"], c["dk"], strided_grad=True)
+    r = REL[c["q"].dtype]
+    assert_close(qe, c["q_out"], r, "q"); assert_close(ke, c["k_out"], r, "k")
+    assert_close(gq, c["dq_in"], r, "dq"); assert_close(gk, c["dk_in"], r, "dk")
+
+
+@pytest.mark.parametrize("b,l,qh,kh,d,theta,dt,batch_cs", [
+    (4, 1024, 14, 2, 64, 1e6, torch.bfloat16, False),   # Qwen2-0.5B shape
+    (4, 1024, 14, 2, 64, 1e6, torch.float32, False),
+    (2, 512, 32, 8, 128, 5e5, torch.bfloat16, False),   # Llama-3-8B heads
+    (2, 256, 28, 4, 128, 1e6, torch.bfloat16, True),    # Qwen2-7B heads, per-batch positions
+    (2, 64, 32, 8, 64, 5e5, torch.float16, False),      # Llama-1B heads
+    (1, 3, 1, 1, 2, 1e4, torch.float32, False),         # smallest legal head
+    (2, 5, 3, 1, 6, 1e4, torch.bfloat16, False),        # scalar path: D/2 not a multiple of the vector
+    (2, 17, 5, 5, 192, 1e4, torch.float32, True),
+    (1, 9, 7, 0, 32, 1e4, torch.bfloat16, False),       # no k heads at all
+])
+def test_rope_vs_oracle(b, l, qh, kh, d, theta, dt, batch_cs):
+    gen = g(b * 1000 + l + d)
+    q = torch.randn(b, qh, l, d, generator=gen).to(dt); k = torch.randn(b, kh, l, d, generator=gen).to(dt)
+    pos = (torch.arange(l)[None] + (torch.arange(b)[:, None] * 3 if batch_cs else 0))
+    cos, sin = E.rope_cos_sin(pos, d, theta, dt)
+    dq = torch.randn(b, qh, l, d, generator=gen).to(dt); dk = torch.randn(b, kh, l, d, generator=gen).to(dt)
+    qe, ke, gq, gk = run_rope(q, k, cos, sin, dq, dk)
+    qo, ko = E.rope_fwd(q, k, cos, sin); gqo, gko = E.rope_bwd(dq, dk, cos, sin)
+    r = REL[dt]
+    assert_close(qe, qo, r, "q"); assert_close(gq, gqo, r, "dq")
+    if kh:
+        assert_close(ke, ko, r, "k"); assert_close(gk, gko, r, "dk")
+    hq, hk = E.hf_rope(q, k, cos, sin)
+    assert_close(qe, hq, r, "q vs HF eager")
+
+
+def test_rope_round_trip_full_size():
+    """Llama-3-8B shape (8 x 4096 tokens): backward(forward(x)) == x because cos^2 + sin^2 == 1; and
+    memory next to the tensors is untouched."""
+    b, l, qh, kh, d = 8, 4096, 32, 8, 128
+    gen = torch.Generator(DEV).manual_seed(1)
+    pad = 1024
+    qbuf = torch.randn(b * l * qh * d + 2 * pad, device=DEV, generator=gen).to(torch.bfloat16)
+    kbuf = torch.randn(b * l * kh * d + 2 * pad, device=DEV, generator=gen).to(torch.bfloat16)
+    q0, k0 = qbuf.clone(), kbuf.clone()
+    q = qbuf[pad:-pad].view(b, l, qh, d).transpose(1, 2); k = kbuf[pad:-pad].view(b, l, kh, d).transpose(1, 2)
+    cos, sin = E.rope_cos_sin(torch.arange(l)[None], d, 5e5, torch.float32)
+    cos, sin = cos.to(DEV).to(torch.bfloat16), sin.to(DEV).to(torch.bfloat16)
+    core.fused_apply_rope(q, k, cos, sin)
+    assert torch.equal(qbuf[:pad], q0[:pad]) and torch.equal(qbuf[-pad:], q0[-pad:])
+    assert torch.equal(kbuf[:pad], k0[:pad]) and torch.equal(kbuf[-pad:], k0[-pad:])
+    assert not torch.equal(qbuf, q0)
+    lib = _C.lib()
+    st = lambda t: (t.stride(0), t.stride(1), t.stride(2))
+    _C.check(lib.mdy_rope(q.data_ptr(), q.data_ptr(), k.data_ptr(), k.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                          b, l, qh, kh, d, 1, *st(q), *st(q), *st(k), *st(k), 1, _C.MDY_BF16,
+                          torch.cuda.current_stream().cuda_stream), "mdy_rope")
+    torch.cuda.synchronize()
+    # two bf16 roundings of O(1) values, cos/sin themselves rounded to bf16
+    assert (qbuf.float() - q0.float()).abs().max() < 0.06
+    assert (kbuf.float() - k0.float()).abs().max() < 0.06
+
+
+# ----------------------------------------------------------------------------------------------- SwiGLU
+@pytest.mark.parametrize("c", golden_cases("swiglu.pt"))
+def test_swiglu_golden(c):
+    r = REL[c["dy"].dtype]
+    if c["kind"] == "split":
+        up, gate = leaf(c["up"]), leaf(c["gate"])
+        y = core.triton_fused_up_gate_silu(up, gate); y.backward(c["dy"].to(DEV))
+        assert_close(y, c["y"], r, "y"); assert_close(up.grad, c["dup"], r, "dup"); assert_close(gate.grad, c["dgate"], r, "dgate")
+    else:
+        x = leaf(c["x"])
+        y = core.triton_fused_up_gate_silu_no_split(x, c["order"]); y.backward(c["dy"].to(DEV))
+        assert_close(y, c["y"], r, "y"); assert_close(x.grad, c["dx"], r, "dx")
+
+
+@pytest.mark.parametrize("shape,dt", [((4096, 4864), torch.bfloat16), ((2, 512, 4864), torch.float32), ((1024, 14336), torch.bfloat16),
+                                      ((3, 1001), torch.float16), ((1, 1), torch.float32), ((5, 7, 9), torch.bfloat16), ((0, 16), torch.bfloat16)])
+def test_swiglu_vs_oracle(shape, dt):
+    gen = g(sum(shape) + 1)
+    up = (torch.randn(*shape, generator=gen) * 2).to(dt); gate = (torch.randn(*shape, generator=gen) * 3).to(dt)
+    dy = torch.randn(*shape, generator=gen).to(dt)
+    ug, gg = leaf(up), leaf(gate)
+    y = core.triton_fused_up_gate_silu(ug, gg); y.backward(dy.to(DEV))
+    r = REL[dt]
+    if y.numel() == 0:
+        assert y.shape == tuple(shape); return
+    assert_close(y, E.swiglu_fwd(up, gate), r, "y")
+    du, dg = E.swiglu_bwd(dy, up, gate)
+    assert_close(ug.grad, du, r, "dup"); assert_close(gg.grad, dg, r, "dgate")
+
+
+def test_swiglu_strided_halves_and_noncontiguous_dy():
+    """up/gate as halves of one projection (row stride 2N) and an expanded (stride-0) upstream gradient,
+    which the reference kernel would mis-read."""
+    gen = g(77)
+    x = torch.randn(64, 2 * 1024, generator=gen).to(torch.bfloat16).to(DEV)
+    up, gate = leaf(x[:, :1024]), leaf(x[:, 1024:])
+    xs = x.clone().requires_grad_(True)
+    y1 = core.triton_fused_up_gate_silu(xs[:, :1024], xs[:, 1024:])
+    y2 = core.triton_fused_up_gate_silu(up, gate)
+    assert torch.equal(y1, y2)
+    y1.sum().backward(); y2.sum().backward()
+    assert torch.equal(xs.grad[:, :1024], up.grad) and torch.equal(xs.grad[:, 1024:], gate.grad)
+    du, dg = E.swiglu_bwd(torch.ones(64, 1024), x[:, :1024].cpu(), x[:, 1024:].cpu())
+    assert_close(up.grad, du, 1e-2); assert_close(gate.grad, dg, 1e-2)
+    for order in ("up-gate", "gate-up"):
+        xn = x.clone().requires_grad_(True)
+        y = core.triton_fused_up_gate_silu_no_split(xn, order)
+        u, gt = E.split_no_split(x.cpu(), order)
+        assert_close(y, E.swiglu_fwd(u, gt), 1e-2, order)
+        y.sum().backward()
+        du, dg = E.swiglu_bwd(torch.ones(64, 1024), u, gt)
+        gu, gg = E.split_no_split(xn.grad, order)
+        assert_close(gu, du, 1e-2); assert_close(gg, dg, 1e-2)
+
+
+def test_swiglu_linearity_full_size():
+    """Qwen2-7B shape: y is linear in `up`, and scaling by 2 is exact in binary floating point."""
+    gen = torch.Generator(DEV).manual_seed(2)
+    up = torch.randn(32768, 18944, device=DEV, generator=gen, dtype=torch.bfloat16)
+    gate = torch.randn(32768, 18944, device=DEV, generator=gen, dtype=torch.bfloat16)
+    y1 = core.triton_fused_up_gate_silu(up, gate)
+    y2 = core.triton_fused_up_gate_silu(up * 2, gate)
+    assert torch.equal(y1 * 2, y2)
+    sample = slice(0, 64)
+    assert_close(y1[sample], E.swiglu_fwd(up[sample].cpu(), gate[sample].cpu()), 1e-2)
+
+
+# ---------------------------------------------------------------------------------------- cross-entropy
+@pytest.mark.parametrize("c", golden_cases("cross_entropy.pt"))
+def test_ce_golden(c):
+    lg, lb = c["logits"], c["labels"].to(DEV)
+    r = REL[lg.dtype]
+    x = leaf(lg)
+    losses = _FastCrossEntropyLoss.apply(x, lb, False)
+    losses.backward(c["dlosses"].to(DEV))
+    assert torch.allclose(losses.cpu(), c["losses"], rtol=LOSS_TOL, atol=LOSS_TOL)
+    assert_close(x.grad, c["dlogits"], r, "dlogits")
+    # in-place variant writes the same gradient into the logits' storage
+    x2 = leaf(lg); xin = x2 * 1.0
+    losses2 = _FastCrossEntropyLoss.apply(xin, lb, True)
+    losses2.backward(c["dlosses"].to(DEV))
+    assert torch.equal(xin.detach(), x.grad)
+    # scalar API (one-pass kernel)
+    x3 = leaf(lg)
+    loss = triton_entropy_loss(x3, lb); loss.backward()
+    loss_close(loss, c["loss"])
+    if "dlogits_scalar" in c:
+        assert_close(x3.grad, c["dlogits_scalar"], r, "dlogits scalar")
+    x4 = leaf(lg)
+    loss_n = core.fast_cross_entropy_loss(x4.view(1, *lg.shape), lb.view(1, -1), n_items=c["n_items"]); loss_n.backward()
+    loss_close(loss_n, c["loss_n"])
+    if "dlogits_n" in c:
+        assert_close(x4.grad, c["dlogits_n"], r, "dlogits n")
+    with torch.no_grad():
+        loss_close(triton_entropy_loss(lg.to(DEV), lb), c["loss"])
+
+
+@pytest.mark.parametrize("m,v,sigma,frac,dt", [
+    (256, 151936, 2.0, 0.05, torch.bfloat16),   # Qwen2 vocab
+    (128, 128256, 3.0, 0.0, torch.bfloat16),    # Llama-3 vocab
+    (128, 152064, 2.0, 0.10, torch.bfloat16),   # Qwen2-7B vocab
+    (64, 256000, 4.0, 0.05, torch.bfloat16),
+    (64, 32000, 1.0, 0.05, torch.float16),
+    (32, 50257, 2.0, 0.1, torch.float32),       # odd vocab, float32
+    (16, 1501, 1.0, 0.2, torch.bfloat16),       # row stride not 16-byte aligned -> scalar path
+    (8, 5, 1.0, 0.0, torch.float32),
+    (4, 1, 1.0, 0.0, torch.float32),
+    (1, 8192, 10.0, 0.0, torch.bfloat16),
+    (7, 1000, 1.0, 1.0, torch.bfloat16),        # every row ignored
+])
+def test_ce_vs_oracle(m, v, sigma, frac, dt):
+    gen = g(m + v)
+    lg = (torch.randn(m, v, generator=gen) * sigma).to(dt)
+    lb = torch.randint(0, v, (m,), generator=gen)
+    lb[torch.rand(m, generator=gen) < frac] = -100
+    dl = torch.randn(m, generator=gen)
+    r = REL[dt]
+    lo, lse_o = E.ce_rows(lg, lb)
+    # two-phase path
+    x = leaf(lg)
+    losses = _FastCrossEntropyLoss.apply(x, lb.to(DEV), False); losses.backward(dl.to(DEV))
+    assert torch.allclose(losses.cpu(), lo, rtol=LOSS_TOL, atol=LOSS_TOL)
+    assert_close(x.grad, E.ce_grad(lg, lb, lse_o, dl), r, "dlogits")
+    # one-pass path, in place and not
+    n = int((lb != -100).sum())
+    for inplace in (False, True):
+        x = leaf(lg); xin = x * 1.0
+        loss = triton_entropy_loss(xin, lb.to(DEV), inplace=inplace); loss.backward()
+        if n == 0:
+            assert torch.isnan(loss)  # 0/0, as in the reference
+            continue
+        loss_close(loss, E.ce_scalar(lg, lb))
+        assert_close(x.grad, E.ce_grad(lg, lb, lse_o, torch.tensor(1.0 / n)), r, f"fused dlogits inplace={inplace}")
+        if inplace:
+            assert torch.equal(xin.detach(), x.grad)
+    if n:
+        loss_close(E.hf_cross_entropy(lg, lb), E.ce_scalar(lg, lb))
+
+
+def test_ce_upstream_gradient_scaling():
+    """loss * 0.25 (gradient accumulation) must scale the gradient the forward already wrote."""
+    gen = g(9)
+    lg = (torch.randn(32, 4096, generator=gen) * 2).to(torch.bfloat16); lb = torch.randint(0, 4096, (32,), generator=gen)
+    x = leaf(lg)
+    (triton_entropy_loss(x, lb.to(DEV)) * 0.25).backward()
+    _, lse = E.ce_rows(lg, lb)
+    assert_close(x.grad, E.ce_grad(lg, lb, lse, torch.tensor(0.25 / 32)), 1e-2)
+
+
+def test_ce_out_of_range_label_and_neg_inf_logits():
+    lg = torch.randn(4, 64) * 2
+    lg[1, 10:20] = float("-inf")
+    lb = torch.tensor([3, 5, 64 + 7, -100])  # row 2: label outside the vocabulary, not -100
+    x = leaf(lg)
+    losses = _FastCrossEntropyLoss.apply(x, lb.to(DEV), False)
+    losses.sum().backward()
+    lo, lse = E.ce_rows(lg, lb)
+    assert torch.allclose(losses.cpu(), lo, atol=1e-5) and losses[2] == 0
+    assert_close(x.grad, E.ce_grad(lg, lb, lse, torch.ones(4)), 1e-4)
+    assert torch.isfinite(x.grad).all()
+
+
+def test_ce_properties_full_size():
+    """Llama-3 shape slice at full vocabulary, 8192 rows (2.1 GB of logits): valid rows of dlogits sum to
+    ~0 (softmax minus one-hot), ignored rows are exactly 0, the label entry is the only negative one,
+    and the one-pass kernel agrees with the two-phase kernels."""
+    m, v = 8192, 128256
+    gen = torch.Generator(DEV).manual_seed(1)
+    lg = (torch.randn(m, v, device=DEV, generator=gen) * 3).to(torch.bfloat16)
+    lb = torch.randint(0, v, (m,), device=DEV, generator=gen)
+    lb[::16] = -100
+    n = int((lb != -100).sum())
+    x = lg.clone().requires_grad_(True)
+    loss = triton_entropy_loss(x, lb); loss.backward()
+    d = x.grad
+    assert (d[::16] == 0).all()
+    valid = lb != -100
+    rows = d[valid].float()
+    assert rows.sum(-1).abs().max() * n < 0.05            # each row of (p - onehot) sums to 0
+    neg = (rows < 0).sum(-1)
+    assert (neg == 1).all()
+    idx = lb[valid]
+    assert (rows.gather(1, idx[:, None]) < 0).all()
+    x2 = lg.clone().requires_grad_(True)
+    l2 = _FastCrossEntropyLoss.apply(x2, lb, False)
+    (l2.sum() / n).backward()
+    loss_close(loss, l2.sum() / n)
+    assert_close(d[:512], x2.grad[:512], 1e-2, "fused vs two-phase")
+    # oracle on a slice the CPU finishes quickly
+    sl = slice(0, 64)
+    lo, lse_o = E.ce_rows(lg[sl].cpu(), lb[sl].cpu())
+    assert torch.allclose(l2[sl].cpu(), lo, rtol=LOSS_TOL, atol=LOSS_TOL)
+    assert_close(d[sl], E.ce_grad(lg[sl].cpu(), lb[sl].cpu(), lse_o, torch.tensor(1.0 / n)), 1e-2)
+
+
+def test_direct_c_abi_calls_with_strides():
+    """Call the entry points directly with row strides larger than the row."""
+    lib = _C.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    gen = g(4)
+    xb = torch.randn(10, 256 + 32, generator=gen).to(torch.bfloat16).to(DEV)
+    w = torch.randn(256, generator=gen).to(torch.bfloat16).to(DEV)
+    yb = torch.zeros(10, 256 + 64, dtype=torch.bfloat16, device=DEV)
+    rstd = torch.empty(10, dtype=torch.float32, device=DEV)
+    _C.check(lib.mdy_rmsnorm_fwd(xb.data_ptr(), w.data_ptr(), yb.data_ptr(), rstd.data_ptr(), 10, 256, 288, 320, 1e-6,
+                                 _C.MDY_BF16, _C.MDY_BF16, st), "fwd")
+    yo, rms = E.rmsnorm_fwd(xb[:, :256].cpu(), w.cpu(), 1e-6)
+    assert_close(yb[:, :256], yo, 1e-2); assert (yb[:, 256:] == 0).all()
+    assert_close(rstd, 1.0 / rms, 1e-5)
+    # cross-entropy with a padded row stride, split mode and a vocab offset
+    v, rs, vs = 1000, 1008, 3000
+    lg = (torch.randn(6, rs, generator=gen) * 2).to(torch.bfloat16).to(DEV)
+    lb = torch.tensor([3000, 3999, 10, 5000, -100, 3500], device=DEV)
+    losses = torch.full((6,), 7.0, device=DEV); lse = torch.full((6,), 7.0, device=DEV)
+    _C.check(lib.mdy_ce_fwd(lg.data_ptr(), lb.data_ptr(), losses.data_ptr(), lse.data_ptr(), 6, v, rs, vs, 1, _C.MDY_BF16, st), "ce_fwd")
+    lo, lse_o = E.ce_rows(lg[:, :v].cpu(), lb.cpu(), vocab_start=vs, split=True)
+    assert torch.allclose(losses.cpu(), lo, atol=1e-4) and torch.allclose(lse.cpu(), lse_o, atol=1e-4)
+    dl = torch.randn(6, generator=gen).to(DEV)
+    out = torch.full_like(lg, 5.0)
+    _C.check(lib.mdy_ce_bwd(dl.data_ptr(), 1, _C.MDY_F32, lg.data_ptr(), out.data_ptr(), lb.data_ptr(), lse.data_ptr(), 6, v, rs, vs, 1,
+                            _C.MDY_BF16, st), "ce_bwd")
+    assert_close(out[:, :v], E.ce_grad(lg[:, :v].cpu(), lb.cpu(), lse_o, dl.cpu(), vocab_start=vs), 1e-2)
+    assert (out[:, v:] == 5.0).all()
+    # combine kernel against the oracle
+    stats = torch.randn(4, 2, 50, generator=gen).to(DEV)
+    lb2 = torch.randint(0, 10, (50,), generator=gen).to(DEV); lb2[::5] = -100
+    l_out = torch.empty(50, device=DEV); s_out = torch.empty(50, device=DEV)
+    _C.check(lib.mdy_ce_vp_combine(stats.data_ptr(), lb2.data_ptr(), l_out.data_ptr(), s_out.data_ptr(), 4, 50, st), "combine")
+    lo, so = E.vp_combine(stats.cpu(), lb2.cpu())
+    assert torch.allclose(l_out.cpu(), lo, atol=1e-5) and torch.allclose(s_out.cpu(), so, atol=1e-5)
+    assert _C.launch_count() > 0

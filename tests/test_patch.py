@@ -1,0 +1,67 @@
+"""``from mdy_triton.replace_kernel import *`` swaps the HuggingFace attributes the reference swaps
+(reference replace_kernel/llama.py:186-190, qwen2.py:200-204), against the installed transformers."""
+import inspect
+
+import torch
+
+import mdy_triton.replace_kernel  # noqa: F401  (the import is the patch)
+from mdy_triton_b200.core.fused_apply_rope import fused_apply_rope
+from mdy_triton_b200.replace_kernel import _common
+
+
+def _check_family(modname, prefix, rope=True):
+    import importlib
+    m = importlib.import_module(f"transformers.models.{modname}.modeling_{modname}")
+    if rope:
+        assert m.apply_rotary_pos_emb is fused_apply_rope
+    assert getattr(m, prefix + "RMSNorm").forward is _common.rmsnorm_forward
+    assert getattr(m, prefix + "MLP").forward.__module__ == _common.__name__
+    dec = getattr(m, prefix + "DecoderLayer").forward
+    lm = getattr(m, prefix + "ForCausalLM").forward
+    assert dec.__module__ == _common.__name__
+    assert "labels" in inspect.signature(lm).parameters
+    assert "hidden_states" in inspect.signature(dec).parameters
+    return m
+
+
+def test_llama_and_qwen2_are_patched():
+    _check_family("llama", "Llama")
+    _check_family("qwen2", "Qwen2")
+
+
+def test_mistral_and_phi3_are_patched():
+    _check_family("mistral", "Mistral")
+    m = _check_family("phi3", "Phi3")
+    assert m.Phi3MLP.forward is _common.mlp_forward_fused_proj
+
+
+def test_reference_import_paths_resolve():
+    from mdy_triton.replace_kernel import trigger
+    from mdy_triton.replace_kernel.llama import module, trigger as t2
+    from mdy_triton.core import (fast_cross_entropy_loss, fused_apply_rope, triton_fused_add_norm,  # noqa: F401
+                                 triton_fused_up_gate_silu, triton_fused_up_gate_silu_no_split, triton_max,
+                                 triton_min, triton_rmsnorm)
+    from mdy_triton.core.cross_entyopy_loss import _FastCrossEntropyLoss, triton_entropy_loss  # noqa: F401
+    from mdy_triton.core.rmsnorm import _TritronRMSNorm  # noqa: F401
+    from mdy_triton.core.fused_add_norm import _TritronFusedAddRMSNorm  # noqa: F401
+    from mdy_triton.core.fused_silu import _FusedSiLU_Unsloth, _FusedSiLUNoSplit  # noqa: F401
+    from mdy_triton.core.fused_apply_rope import _FusedApplyRope  # noqa: F401
+    assert trigger is None and t2 is None and module.__name__.endswith("modeling_llama")
+
+
+def test_shifted_labels():
+    lb = torch.tensor([[1, 2, 3, 4], [5, 6, -100, 8]])
+    out = _common.shifted_labels(lb)
+    assert out.tolist() == [[2, 3, 4, -100], [6, -100, 8, -100]]
+
+
+def test_patched_model_builds_on_cpu_and_refuses_to_run_there():
+    """The patch must not break model construction; running on CPU must raise (no fallback)."""
+    import pytest
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+                      num_key_value_heads=2, vocab_size=128, max_position_embeddings=64)
+    model = LlamaForCausalLM(cfg)
+    ids = torch.randint(0, 128, (1, 8))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        model(input_ids=ids, labels=ids)
