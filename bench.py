@@ -1,0 +1,453 @@
+#!/usr/bin/env python
+"""Benchmark of the fused-operator path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c1|c2|c3]
+
+One step = forward + backward of the fused operator set at one BASELINE config (default c2, the
+Llama-3-8B-shaped set: add+RMSNorm [32768,4096], RoPE 32q/8kv heads x 128, SwiGLU [32768,14336],
+cross-entropy [32768,128256], bf16) on synthetic seeded inputs.  Every rank owns its own 32768-token
+shard (tokens are independent: no data-path collective), so the job is weak-scaled.
+
+Printed JSON (rank 0, one line):
+  value      aggregate algorithmic HBM GB/s over all ranks, inputs resident in HBM, kernels launched
+             through the C-ABI, timed with CUDA events (max over ranks)
+  per_op     the same per operator, with its fraction of the measured HBM peak
+  roofline   the dominant kernel (one-pass cross-entropy)
+  e2e        the same metric through the public operator API with inputs in pinned HOST memory:
+             host->device copies of every step's inputs and the device->host read of the loss are
+             inside the timed region
+  cpu_baseline  the float32 CPU oracle (HF-eager-equivalent math, autograd) on a bounded token sample
+
+`--impl reference` times the CPU oracle only (the reference has no CPU implementation of its own; its
+Triton kernels need a GPU and its sources do not travel to the benchmark machine).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CONFIGS = {
+    # name: tokens(B, L), hidden, eps, (QH, KH, D, theta), ffn, vocab, sigma, ignored fraction, seed, norm kind
+    "c1": dict(desc="Qwen2-0.5B-shaped op set", B=4, L=1024, hidden=896, eps=1e-6, QH=14, KH=2, D=64, theta=1e6,
+               ffn=4864, vocab=151936, sigma=2.0, ignored=0.05, seed=0, norm="rmsnorm"),
+    "c2": dict(desc="Llama-3-8B-shaped op set", B=8, L=4096, hidden=4096, eps=1e-5, QH=32, KH=8, D=128, theta=5e5,
+               ffn=14336, vocab=128256, sigma=3.0, ignored=0.0, seed=1, norm="add_rmsnorm"),
+    "c3": dict(desc="Qwen2-7B-shaped op set", B=16, L=2048, hidden=3584, eps=1e-6, QH=28, KH=4, D=128, theta=1e6,
+               ffn=18944, vocab=152064, sigma=2.0, ignored=0.10, seed=2, norm="rmsnorm"),
+}
+OPS = ("norm", "rope", "swiglu", "cross_entropy")
+FALLBACK_PEAK_GBS = 6650.0
+# dram__bytes_read.sum + dram__bytes_write.sum of one one-pass cross-entropy launch, from the ncu capture
+# summarised under profiles/ (None until a capture exists): bytes per row of the captured case.
+CE_TRAFFIC_BYTES_PER_ROW = None
+
+
+def algorithmic_bytes(cfg, tokens, ignored_frac, s=2):
+    """Bytes each operator must move for forward+backward (one read or write per tensor element that the
+    math needs): norm 5*M*N*s (RMSNorm) or 8*M*N*s (add+RMSNorm, one shared gradient tensor);
+    RoPE 4*T*(QH+KH)*D*s + 4*L*D*s (cos/sin broadcast over batch); SwiGLU 8*M*N*s;
+    cross-entropy M*V*s*(2 - f_ignored) + 16*M (labels, losses, lse)."""
+    M = tokens
+    nb = (8 if cfg["norm"] == "add_rmsnorm" else 5) * M * cfg["hidden"] * s
+    rb = 4 * M * (cfg["QH"] + cfg["KH"]) * cfg["D"] * s + 4 * cfg["L"] * cfg["D"] * s
+    sb = 8 * M * cfg["ffn"] * s
+    cb = M * cfg["vocab"] * s * (2 - ignored_frac) + 16 * M
+    return {"norm": nb, "rope": rb, "swiglu": sb, "cross_entropy": cb}
+
+
+def measured_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+        except Exception:
+            pass
+    return FALLBACK_PEAK_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+# ------------------------------------------------------------------------------------------------ clocks
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        self.index = index
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1])); pw.append(float(parts[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        # samples under load = those in the upper half of the power range seen
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "power_w_max": max(pw),
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ------------------------------------------------------------------------------------------- device arm
+class OpSet:
+    """Device buffers of one config shard plus direct C-ABI launches (no autograd, no allocation in the
+    timed loop)."""
+
+    def __init__(self, cfg, dev, seed):
+        from mdy_triton_b200 import _C
+        self.C, self.lib, self.cfg, self.dev = _C, _C.lib(), cfg, dev
+        dt = torch.bfloat16
+        g = torch.Generator(dev).manual_seed(seed)
+        B, L, H = cfg["B"], cfg["L"], cfg["hidden"]
+        M = self.M = B * L
+
+        def rn(*shape, scale=1.0):
+            t = torch.randn(*shape, device=dev, generator=g, dtype=dt)
+            return t if scale == 1.0 else t.mul_(scale)
+        # norm
+        self.x = rn(M, H); self.res = rn(M, H); self.w = (1 + 0.02 * torch.randn(H, device=dev, generator=g)).to(dt)
+        self.y = torch.empty_like(self.x); self.nres = torch.empty_like(self.x)
+        self.rstd = torch.empty(M, dtype=torch.float32, device=dev)
+        self.dy = rn(M, H); self.dnres = rn(M, H); self.dx = torch.empty_like(self.x); self.dw = torch.empty_like(self.w)
+        rows = self.lib.mdy_rmsnorm_bwd_partial_rows(M, H, _C.MDY_BF16)
+        self.partial = torch.empty(rows, H, dtype=torch.float32, device=dev)
+        # rope: storage [B, L, H, D]
+        QH, KH, D = cfg["QH"], cfg["KH"], cfg["D"]
+        self.q = rn(B, L, QH, D); self.k = rn(B, L, KH, D)
+        self.dq = rn(B, L, QH, D); self.dk = rn(B, L, KH, D)
+        self.dq_out = torch.empty_like(self.q); self.dk_out = torch.empty_like(self.k)
+        # cos/sin tables the way HF builds them: inv_freq = theta^(-2i/D), emb = cat(freqs, freqs), [1, L, D]
+        inv_freq = 1.0 / (cfg["theta"] ** (torch.arange(0, D, 2, dtype=torch.float32, device=dev) / D))
+        freqs = torch.arange(L, dtype=torch.float32, device=dev)[None, :, None] * inv_freq
+        emb = torch.cat((freqs, freqs), dim=-1)
+        self.cos = emb.cos().to(dt).contiguous(); self.sin = emb.sin().to(dt).contiguous()
+        # swiglu
+        F = cfg["ffn"]
+        self.up = rn(M, F); self.gate = rn(M, F); self.sy = torch.empty_like(self.up)
+        self.sdy = rn(M, F); self.dup = torch.empty_like(self.up); self.dgate = torch.empty_like(self.up)
+        # cross-entropy
+        V = cfg["vocab"]
+        self.logits = rn(M, V, scale=cfg["sigma"])
+        self.labels = torch.randint(0, V, (M,), device=dev, generator=g)
+        if cfg["ignored"] > 0:
+            self.labels[torch.rand(M, device=dev, generator=g) < cfg["ignored"]] = -100
+        self.ignored_frac = float((self.labels == -100).float().mean())
+        self.dlogits = torch.empty_like(self.logits)
+        self.losses = torch.empty(M, dtype=torch.float32, device=dev); self.lse = torch.empty(M, dtype=torch.float32, device=dev)
+        self.inv_n = (1.0 / torch.count_nonzero(self.labels != -100).float()).reshape(1)
+        self.stream = torch.cuda.current_stream(dev).cuda_stream
+
+    def _st(self, t):  # (batch, head, position) strides of a [B, L, H, D] storage viewed as [B, H, L, D]
+        return t.stride(0), t.stride(2), t.stride(1)
+
+    def norm(self):
+        C, lib, c, st = self.C, self.lib, self.cfg, self.stream
+        M, H, bf = self.M, c["hidden"], C.MDY_BF16
+        if c["norm"] == "add_rmsnorm":
+            C.check(lib.mdy_add_rmsnorm_fwd(self.x.data_ptr(), self.res.data_ptr(), self.w.data_ptr(), self.y.data_ptr(),
+                                            self.nres.data_ptr(), self.rstd.data_ptr(), M, H, H, c["eps"], bf, bf, st), "add_rmsnorm_fwd")
+            C.check(lib.mdy_add_rmsnorm_bwd(self.dy.data_ptr(), self.dnres.data_ptr(), self.nres.data_ptr(), self.w.data_ptr(),
+                                            self.rstd.data_ptr(), self.dx.data_ptr(), self.dw.data_ptr(), self.partial.data_ptr(),
+                                            M, H, H, bf, bf, st), "add_rmsnorm_bwd")
+        else:
+            C.check(lib.mdy_rmsnorm_fwd(self.x.data_ptr(), self.w.data_ptr(), self.y.data_ptr(), self.rstd.data_ptr(), M, H, H, H,
+                                        c["eps"], bf, bf, st), "rmsnorm_fwd")
+            C.check(lib.mdy_rmsnorm_bwd(self.dy.data_ptr(), self.x.data_ptr(), self.w.data_ptr(), self.rstd.data_ptr(),
+                                        self.dx.data_ptr(), self.dw.data_ptr(), self.partial.data_ptr(), M, H, H, H, H, bf, bf, st),
+                    "rmsnorm_bwd")
+
+    def rope(self):
+        C, lib, c, st = self.C, self.lib, self.cfg, self.stream
+        a = (c["B"], c["L"], c["QH"], c["KH"], c["D"], 1)
+        C.check(lib.mdy_rope(self.q.data_ptr(), self.q.data_ptr(), self.k.data_ptr(), self.k.data_ptr(), self.cos.data_ptr(),
+                             self.sin.data_ptr(), *a, *self._st(self.q), *self._st(self.q), *self._st(self.k), *self._st(self.k),
+                             0, C.MDY_BF16, st), "rope fwd")
+        C.check(lib.mdy_rope(self.dq.data_ptr(), self.dq_out.data_ptr(), self.dk.data_ptr(), self.dk_out.data_ptr(),
+                             self.cos.data_ptr(), self.sin.data_ptr(), *a, *self._st(self.dq), *self._st(self.dq_out),
+                             *self._st(self.dk), *self._st(self.dk_out), 1, C.MDY_BF16, st), "rope bwd")
+
+    def swiglu(self):
+        C, lib, c, st = self.C, self.lib, self.cfg, self.stream
+        M, F = self.M, c["ffn"]
+        C.check(lib.mdy_swiglu_fwd(self.up.data_ptr(), self.gate.data_ptr(), self.sy.data_ptr(), M, F, F, F, F, C.MDY_BF16, st), "swiglu_fwd")
+        C.check(lib.mdy_swiglu_bwd(self.sdy.data_ptr(), self.up.data_ptr(), self.gate.data_ptr(), self.dup.data_ptr(),
+                                   self.dgate.data_ptr(), M, F, F, F, F, F, F, C.MDY_BF16, st), "swiglu_bwd")
+
+    def cross_entropy(self):
+        C, lib, c, st = self.C, self.lib, self.cfg, self.stream
+        C.check(lib.mdy_ce_fused(self.logits.data_ptr(), self.dlogits.data_ptr(), self.labels.data_ptr(), self.losses.data_ptr(),
+                                 self.lse.data_ptr(), self.inv_n.data_ptr(), 1.0, self.M, c["vocab"], c["vocab"], C.MDY_BF16, st),
+                "ce_fused")
+
+    def step(self, events=None):
+        for i, name in enumerate(OPS):
+            getattr(self, name)()
+            if events is not None:
+                events[i + 1].record()
+
+
+def run_device_arm(ops: OpSet, steps, warmup, barrier):
+    for _ in range(warmup):
+        ops.step()
+    torch.cuda.synchronize()
+    barrier()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(OPS) + 1)] for _ in range(steps)]
+    l0 = ops.C.launch_count()
+    torch.cuda.synchronize()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for s in range(steps):
+        ev[s][0].record()
+        ops.step(ev[s])
+    t1.record()
+    torch.cuda.synchronize()
+    barrier()
+    total_ms = t0.elapsed_time(t1)
+    per_op_ms = {name: statistics.mean(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(steps)) for i, name in enumerate(OPS)}
+    return total_ms, per_op_ms, ops.C.launch_count() - l0
+
+
+# --------------------------------------------------------------------------------------------- e2e arm
+def run_e2e_arm(ops: OpSet, steps, warmup, barrier):
+    """Public operator API (autograd functions of mdy_triton.core) with the step's inputs in pinned host
+    memory: H2D of every input, forward+backward of the four operators, D2H of the loss."""
+    import mdy_triton.core as core
+    cfg, dev = ops.cfg, ops.dev
+    names = ["x", "res", "q", "k", "up", "gate", "logits", "labels"]
+    host = {n: torch.empty(getattr(ops, n).shape, dtype=getattr(ops, n).dtype, pin_memory=True).copy_(getattr(ops, n)) for n in names}
+    h2d = sum(t.numel() * t.element_size() for t in host.values())
+    loss_host = torch.empty(1, dtype=torch.float32, pin_memory=True)
+    w = ops.w.clone().requires_grad_(True)
+    B, L = cfg["B"], cfg["L"]
+
+    def one_step():
+        d = {n: getattr(ops, n) for n in names}
+        for n in names:
+            d[n].copy_(host[n], non_blocking=True)
+        x = d["x"].requires_grad_(True)
+        if cfg["norm"] == "add_rmsnorm":
+            res = d["res"].requires_grad_(True)
+            y, nres = core.triton_fused_add_norm(x, res, w, cfg["eps"])
+            torch.autograd.backward([y, nres], [ops.dy, ops.dnres])
+        else:
+            y = core.triton_rmsnorm(x, w, cfg["eps"])
+            y.backward(ops.dy)
+        q = d["q"].requires_grad_(True); k = d["k"].requires_grad_(True)
+        qe, ke = core.fused_apply_rope(q.transpose(1, 2), k.transpose(1, 2), ops.cos, ops.sin)
+        torch.autograd.backward([qe, ke], [ops.dq.transpose(1, 2), ops.dk.transpose(1, 2)])
+        up = d["up"].requires_grad_(True); gate = d["gate"].requires_grad_(True)
+        sy = core.triton_fused_up_gate_silu(up, gate)
+        sy.backward(ops.sdy)
+        logits = d["logits"].requires_grad_(True)
+        loss = core.triton_entropy_loss(logits.view(B, L, -1), d["labels"].view(B, L))
+        loss.backward()
+        loss_host.copy_(loss.detach().reshape(1), non_blocking=True)
+        for n in ("x", "res", "q", "k", "up", "gate", "logits"):
+            d[n].requires_grad_(False); d[n].grad = None
+        w.grad = None
+
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        one_step()
+    t1.record()
+    torch.cuda.synchronize()
+    barrier()
+    return t0.elapsed_time(t1) / steps, h2d, 4, float(loss_host[0])
+
+
+# ----------------------------------------------------------------------------------------- CPU baseline
+def cpu_oracle_step(cfg, tokens, seed):
+    """Forward+backward of the four operators in float32 on the host (HF-eager-equivalent autograd math
+    from oracle/eager.py) for `tokens` tokens of the config.  Returns a closure that runs one step."""
+    from oracle import eager as E
+    g = torch.Generator().manual_seed(seed)
+    L = min(cfg["L"], tokens); B = max(1, tokens // L); M = B * L
+    H, F, V, D = cfg["hidden"], cfg["ffn"], cfg["vocab"], cfg["D"]
+    x = torch.randn(M, H, generator=g); res = torch.randn(M, H, generator=g); w = 1 + 0.02 * torch.randn(H, generator=g)
+    dy = torch.randn(M, H, generator=g); dn = torch.randn(M, H, generator=g)
+    q = torch.randn(B, cfg["QH"], L, D, generator=g); k = torch.randn(B, cfg["KH"], L, D, generator=g)
+    dq = torch.randn(B, cfg["QH"], L, D, generator=g); dk = torch.randn(B, cfg["KH"], L, D, generator=g)
+    cos, sin = E.rope_cos_sin(torch.arange(L)[None], D, cfg["theta"])
+    up = torch.randn(M, F, generator=g); gate = torch.randn(M, F, generator=g); sdy = torch.randn(M, F, generator=g)
+    logits = torch.randn(M, V, generator=g) * cfg["sigma"]
+    labels = torch.randint(0, V, (M,), generator=g)
+    if cfg["ignored"] > 0:
+        labels[torch.rand(M, generator=g) < cfg["ignored"]] = -100
+    ign = float((labels == -100).float().mean())
+
+    def step():
+        if cfg["norm"] == "add_rmsnorm":
+            E.autograd_add_rmsnorm(x, res, w, cfg["eps"], dy, dn)
+        else:
+            E.autograd_rmsnorm(x, w, cfg["eps"], dy)
+        E.autograd_rope(q, k, cos, sin, dq, dk)
+        E.autograd_swiglu(up, gate, sdy)
+        return E.autograd_ce(logits, labels)[0]
+
+    return step, M, ign
+
+
+def run_cpu_baseline(cfg, tokens, steps, warmup, seed):
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
+    step, M, ign = cpu_oracle_step(cfg, tokens, seed)
+    for _ in range(warmup):
+        step()
+    t = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t) / steps
+    nbytes = sum(algorithmic_bytes(cfg, M, ign).values())
+    return nbytes / dt / 1e9, dt, M, torch.get_num_threads()
+
+
+# -------------------------------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-tokens", type=int, default=8192)
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="override the tokens per GPU (a multiple of the config's sequence length); smaller "
+                         "cases are for profiler captures, not for reported numbers")
+    args = ap.parse_args()
+    cfg = dict(CONFIGS[args.config])
+    if args.tokens:
+        if args.tokens % cfg["L"]:
+            raise SystemExit(f"--tokens must be a multiple of the sequence length {cfg['L']}")
+        cfg["B"] = args.tokens // cfg["L"]
+    warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    workload = (f"{cfg['desc']} fwd+bwd, bf16, seed {cfg['seed']}, {cfg['B']}x{cfg['L']} tokens per GPU: "
+                f"{'add+RMSNorm' if cfg['norm'] == 'add_rmsnorm' else 'RMSNorm'} hidden {cfg['hidden']}; RoPE "
+                f"{cfg['QH']}q/{cfg['KH']}kv x {cfg['D']}; SwiGLU {cfg['ffn']}; cross-entropy vocab {cfg['vocab']}")
+    config = {"workload": workload, "tokens_per_gpu": cfg["B"] * cfg["L"], "sharding": "tokens, one shard per GPU, no collective",
+              "l2": "every tensor streamed per step is larger than the 126 MB L2 (no flush needed)"}
+    metric, unit = "fused_opset_fwd_bwd_algorithmic_hbm_throughput", "GB/s"
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        gbs, dt, M, cores = run_cpu_baseline(cfg, args.cpu_tokens, max(1, args.steps), max(0, args.warmup), cfg["seed"])
+        sample = f"{M} of {cfg['B'] * cfg['L']} tokens per step, all four ops fwd+bwd, float32 autograd on host"
+        print(json.dumps({"impl": "reference", "metric": metric, "value": gbs, "unit": unit, "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+                          "cpu_baseline": {"value": gbs, "unit": unit, "cores": cores, "kind": "port", "sample": sample},
+                          "e2e": {"value": gbs, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                          "gpu_launches": 0}))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the operators)")
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+
+    def max_over_ranks(v):
+        if dist is None:
+            return v
+        t = torch.tensor([v], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t[0])
+
+    ops = OpSet(cfg, dev, cfg["seed"] + rank)
+    ab = algorithmic_bytes(cfg, ops.M, ops.ignored_frac)
+    step_bytes = sum(ab.values())
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    total_ms, per_op_ms, launches = run_device_arm(ops, args.steps, warmup, barrier)
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = max_over_ranks(total_ms)
+    ms_per_step = total_ms / args.steps
+    value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
+    peak, peak_src = measured_peak()
+    per_op = {n: {"ms": per_op_ms[n], "GB/s": ab[n] / (per_op_ms[n] * 1e-3) / 1e9,
+                  "frac_of_peak": ab[n] / (per_op_ms[n] * 1e-3) / 1e9 / peak, "algorithmic_bytes": ab[n]} for n in OPS}
+
+    e2e = None
+    if not args.no_e2e:
+        e_ms, h2d, d2h, loss = run_e2e_arm(ops, min(args.steps, 5), 1, barrier)
+        e_ms = max_over_ranks(e_ms)
+        e2e = {"value": world * step_bytes / (e_ms * 1e-3) / 1e9, "unit": unit, "h2d_bytes_per_step": h2d,
+               "d2h_bytes_per_step": d2h, "ms_per_step": e_ms, "loss": loss}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        gbs, dt, M, cores = run_cpu_baseline(cfg, args.cpu_tokens, 2, 1, cfg["seed"])
+        cpu = {"value": gbs, "unit": unit, "cores": cores, "kind": "port",
+               "sample": f"{M} of {ops.M} tokens, all four ops fwd+bwd, float32 autograd on host, {dt:.2f} s per pass"}
+
+    if rank == 0:
+        ce = per_op["cross_entropy"]
+        traffic = None if CE_TRAFFIC_BYTES_PER_ROW is None else CE_TRAFFIC_BYTES_PER_ROW * ops.M
+        out = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+               "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+               "data": "synthetic", "config": config, "frac_of_peak": value / world / peak, "per_op": per_op,
+               "roofline": {"kernel": "one-pass cross-entropy (mdy_ce_fused)", "bound": "hbm", "achieved": ce["GB/s"], "peak": peak,
+                            "peak_source": peak_src, "unit": "GB/s", "frac": ce["GB/s"] / peak, "traffic": traffic},
+               "clocks": clocks, "gpu_launches": launches}
+        if e2e is not None:
+            out["e2e"] = e2e
+        if cpu is not None:
+            out["cpu_baseline"] = cpu
+        print(json.dumps(out))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

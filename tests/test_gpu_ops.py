@@ -46,7 +46,7 @@ def test_rmsnorm_golden(c):
 
 @pytest.mark.parametrize("m,n,dt", [(4096, 896, torch.bfloat16), (4096, 896, torch.float32), (2048, 3584, torch.bfloat16),
                                     (1024, 2048, torch.float16), (1, 4096, torch.bfloat16), (3, 8, torch.float32),
-                                    (5, 1, torch.float32), (7, 7, torch.bfloat16), (9, 127, torch.float16),
+                                    (7, 7, torch.bfloat16), (9, 127, torch.float16),
                                     (9, 129, torch.bfloat16), (64, 3585, torch.bfloat16), (300, 8192, torch.bfloat16),
                                     (40, 16384, torch.bfloat16), (12, 32768, torch.bfloat16), (6, 65536, torch.bfloat16),
                                     (4, 70000, torch.float32), (33, 5120, torch.float32)])
@@ -60,6 +60,17 @@ def test_rmsnorm_vs_oracle(m, n, dt):
     r = REL[dt]
     assert_close(y, yo, r, "y"); assert_close(dx, dxo, r, "dx")
     assert_close(dw, dwo, max(r, 2e-3) if dt == torch.float32 else r, "dw")
+
+
+def test_rmsnorm_single_column():
+    """N == 1: y = sign(x) * w up to eps; dx cancels to ~0 (it is rounding noise relative to w*dy/rms)."""
+    x = torch.tensor([[0.5], [-2.0], [3.0], [1e-2], [-7.0]]); w = torch.tensor([1.5]); dy = torch.randn(5, 1, generator=g(1))
+    y, dx, dw = run_rmsnorm(x, w, 1e-6, dy)
+    yo, rms = E.rmsnorm_fwd(x, w, 1e-6)
+    dxo, dwo = E.rmsnorm_bwd(dy, x, w, 1e-6)
+    assert_close(y, yo, 1e-4, "y"); assert_close(dw, dwo, 1e-4, "dw")
+    bound = 1e-5 * (w * dy).abs() / rms[:, None]
+    assert ((dx.cpu() - dxo).abs() <= bound).all()
 
 
 def test_rmsnorm_3d_input_strided_rows_and_fp32_weight():
