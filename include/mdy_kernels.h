@@ -62,8 +62,16 @@ const char* mdy_status_string(int status);
 #define MDY_TUNE_SWIGLU_UNROLL 3     /* 16-byte vectors per thread in SwiGLU (1, 2 or 4)           */
 #define MDY_TUNE_CE_FUSED_IMPL 4     /* 0 auto, 1 L2-resident row kernel, 2 cluster/shared-memory kernel */
 #define MDY_TUNE_ROPE_THREADS 5      /* threads per CTA of the RoPE kernel                         */
-#define MDY_TUNE_COUNT 6
+#define MDY_TUNE_CE_CLUSTER_SLICE_KB 6 /* largest slice of a row one CTA of the cluster kernel stages (KiB) */
+#define MDY_TUNE_CE_CLUSTER_THREADS 7  /* threads per CTA of the cluster kernel: 512 or 1024          */
+#define MDY_TUNE_CE_CLUSTER_VPC 8      /* 16-byte vectors per thread per chunk there: 1, 2 or 4       */
+#define MDY_TUNE_COUNT 9
 int mdy_set_tunable(int id, int value);
+/* Kernels that wait on hardware barriers bound every wait; if one ever expires they record a non-zero
+ * code in a device flag and run to completion with a wrong result instead of hanging.  This call
+ * synchronises with the device, returns the flag (0 = no such event, -1 = the flag could not be
+ * read) and resets it when clear != 0.  For tests and diagnostics; not needed on the hot path. */
+int mdy_last_device_error(int clear);
 int mdy_get_tunable(int id);
 
 /* ---- RMSNorm ------------------------------------------------------------------------------ */

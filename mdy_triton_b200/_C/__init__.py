@@ -24,6 +24,9 @@ TUNE_NORM_CTAS_PER_SM = 2
 TUNE_SWIGLU_UNROLL = 3
 TUNE_CE_FUSED_IMPL = 4
 TUNE_ROPE_THREADS = 5
+TUNE_CE_CLUSTER_SLICE_KB = 6
+TUNE_CE_CLUSTER_THREADS = 7
+TUNE_CE_CLUSTER_VPC = 8
 
 _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 
@@ -35,6 +38,7 @@ SIGNATURES = {
     "mdy_status_string": (c_char_p, [_I]),
     "mdy_set_tunable": (_I, [_I, _I]),
     "mdy_get_tunable": (_I, [_I]),
+    "mdy_last_device_error": (_I, [_I]),
     "mdy_rmsnorm_bwd_partial_rows": (_L, [_L, _L, _I]),
     "mdy_rmsnorm_fwd": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _F, _I, _I, _P]),
     "mdy_rmsnorm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _I, _I, _P]),

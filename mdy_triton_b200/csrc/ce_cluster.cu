@@ -1,11 +1,473 @@
 // One-pass cross-entropy with the row staged in shared memory across a thread-block cluster.
+//
+// A row of V logits (256 KB at V = 128256 in bf16) does not fit one SM's shared memory, so a cluster
+// of C CTAs (C = 1..8, chosen so a slice is <= 200 KB) owns a row: CTA c keeps slice c of the row in
+// its shared memory.  The slice is fetched by the bulk-copy engine (cp.async.bulk, one mbarrier per
+// chunk) so HBM reads run ahead of the math without occupying registers.
+//   sweep 1: as each chunk lands, every thread folds its 16 bytes into a running (max, sum-exp);
+//            the CTA reduces through warp shuffles + shared memory, the CTAs of the cluster exchange
+//            their partial (max, sum, label logit) through distributed shared memory.
+//   sweep 2: the slice is read again FROM SHARED MEMORY, (softmax - onehot) * g is written to global
+//            memory with streaming stores; as soon as a chunk has been consumed, the bulk copy of the
+//            same chunk of the cluster's NEXT row is issued into it, so loads of row i+1 overlap the
+//            exp/store work of row i.
+// HBM therefore sees exactly one read and one write per logit, independent of L2 residency.
+// Clusters are persistent and take rows round-robin; rows labelled MDY_IGNORE_INDEX are zero-filled
+// without being read.  No multicast copy is used anywhere.
+//
+// Every wait on an mbarrier is bounded: if it expires the kernel records a code in a device flag
+// (mdy_last_device_error) and carries on, so a logic error shows up as a flagged wrong result, never
+// as a hang.
+#include <math.h>
 #include "common.cuh"
 
 namespace mdy {
+namespace {
 
-int ce_fused_cluster(const void*, void*, const int64_t*, float*, float*, const float*, float, int64_t,
-                     int64_t, int64_t, int, cudaStream_t) {
-  return MDY_ERR_UNSUPPORTED;
+constexpr int kMaxChunks = 32;
+constexpr int kMaxCluster = 8;
+
+__device__ int g_dev_error = 0;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// `dead` is per-thread state: after one wait has expired the thread stops waiting altogether, so a
+// broken pipeline costs one bounded wait in total, not one per chunk and row.
+__device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, bool& dead) {
+  if (dead) return;
+  // each try_wait may suspend for up to ~1 us; 2^20 tries bound the wait to about a second
+  for (int i = 0; i < (1 << 20); ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(1000u)
+        : "memory");
+    if (ok) return;
+  }
+  dead = true;
+  atomicExch(&g_dev_error, 1);
+}
+// global -> this CTA's shared memory, completion signalled on `bar` (non-multicast bulk copy)
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+               "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void st_remote_f32(uint32_t local_addr, uint32_t rank, float v) {
+  uint32_t ra;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// (m, s) <- merge with (om, os): one exp per merge; -inf maxima carry s == 0
+__device__ __forceinline__ void merge1(float& m, float& s, float om, float os) {
+  if (om > m) {
+    s = ((m == -INFINITY) ? 0.f : s * fast_exp2((m - om) * kLog2e)) + os;
+    m = om;
+  } else if (om != -INFINITY) {
+    s += os * fast_exp2((om - m) * kLog2e);
+  }
+}
+
+// A 16-byte vector whose every element is -inf: padding that changes neither a max nor a sum of exps.
+template <typename T> __device__ __forceinline__ uint4 neg_inf_vec();
+template <> __device__ __forceinline__ uint4 neg_inf_vec<float>() { return make_uint4(0xff800000u, 0xff800000u, 0xff800000u, 0xff800000u); }
+template <> __device__ __forceinline__ uint4 neg_inf_vec<__nv_bfloat16>() { return make_uint4(0xff80ff80u, 0xff80ff80u, 0xff80ff80u, 0xff80ff80u); }
+template <> __device__ __forceinline__ uint4 neg_inf_vec<__half>() { return make_uint4(0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u, 0xfc00fc00u); }
+
+// max of the elements of one vector, using packed 16-bit max where the type allows (4 instead of 7
+// float max operations per 8 elements)
+template <typename T> __device__ __forceinline__ float vec_max(const uint4& q);
+template <> __device__ __forceinline__ float vec_max<float>(const uint4& q) {
+  return fmaxf(fmaxf(__uint_as_float(q.x), __uint_as_float(q.y)), fmaxf(__uint_as_float(q.z), __uint_as_float(q.w)));
+}
+template <> __device__ __forceinline__ float vec_max<__nv_bfloat16>(const uint4& q) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+  const __nv_bfloat162 a = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+  const uint32_t w = *reinterpret_cast<const uint32_t*>(&a);
+  return fmaxf(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+template <> __device__ __forceinline__ float vec_max<__half>(const uint4& q) {
+  const __half2* h = reinterpret_cast<const __half2*>(&q);
+  const __half2 a = __hmax2(__hmax2(h[0], h[1]), __hmax2(h[2], h[3]));
+  return fmaxf(__low2float(a), __high2float(a));
+}
+
+struct ClusterArgs {
+  const void* logits; void* dlogits; const int64_t* labels; float* losses; float* lse;
+  const float* gdev; float ghost;
+  int M; int64_t V; int64_t rs;
+  int C;        // CTAs per cluster
+  int vpc;      // 16-byte vectors per CTA slice
+  int slice_bytes_aligned;
+};
+
+// Branch-free merge of (m, s) with (om, os): one exp, no divergence.  Maxima are clamped to -1e37 so
+// two empty operands (-inf, 0) do not produce inf - inf.
+__device__ __forceinline__ void merge_nb(float& m, float& s, float om, float os) {
+  const float a = fmaxf(m, -1e37f), b = fmaxf(om, -1e37f);
+  const float e = fast_exp2(-fabsf(a - b) * kLog2e);
+  s = (a >= b) ? fmaf(os, e, s) : fmaf(s, e, os);
+  m = fmaxf(m, om);
+}
+
+// Sweep-1 work on VPC vectors already in registers: one max/rescale per call, then 8*VPC exps
+// accumulated in two independent sums.
+template <typename T, int VPC>
+__device__ __forceinline__ void stats_chunk(const uint4 (&q)[VPC], float& m, float& s0, float& s1) {
+  constexpr int VE = VecInfo<T>::kElems;
+  float vm = vec_max<T>(q[0]);
+#pragma unroll
+  for (int j = 1; j < VPC; ++j) vm = fmaxf(vm, vec_max<T>(q[j]));
+  if (vm > m) {  // rare after the first chunks
+    const float r = fast_exp2((fmaxf(m, -1e37f) - vm) * kLog2e);  // empty so far: s == 0, r == 0
+    s0 *= r; s1 *= r;
+    m = vm;
+  }
+  const float nm2 = -fmaxf(m, -1e37f) * kLog2e;  // finite even when everything so far is -inf
+#pragma unroll
+  for (int j = 0; j < VPC; ++j) {
+    float f[VE];
+    unpack<T>(q[j], f);
+#pragma unroll
+    for (int e = 0; e < VE; e += 2) {
+      s0 += fast_exp2(fmaf(f[e], kLog2e, nm2));
+      s1 += fast_exp2(fmaf(f[e + 1], kLog2e, nm2));
+    }
+  }
+}
+
+// Sweep-2 work on one vector: exp2(x*log2e + c) for every element, packed for the store.  With FOLD
+// the gradient scale g is already inside c; otherwise it is multiplied in.
+template <typename T, bool FOLD>
+__device__ __forceinline__ uint4 grad_vec(const uint4& q, float c, float g) {
+  constexpr int VE = VecInfo<T>::kElems;
+  float f[VE];
+  unpack<T>(q, f);
+#pragma unroll
+  for (int e = 0; e < VE; ++e) {
+    f[e] = fast_exp2(fmaf(f[e], kLog2e, c));
+    if (!FOLD) f[e] *= g;
+  }
+  return pack<T>(f);
+}
+
+// NT threads per CTA, VPC vectors per thread per chunk: a chunk is NT*VPC*16 bytes.
+// FOLD: the gradient scale g is positive and finite, so (p - onehot)*g is computed as
+// exp2(x*log2e - lse*log2e + log2 g) - onehot*g and costs no multiply per element.
+template <typename T, int NT, int VPC, bool FOLD>
+__device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char* smem_raw, float g) {
+  constexpr int VE = VecInfo<T>::kElems;
+  constexpr int CV = NT * VPC;            // vectors per chunk
+  constexpr int NW = NT / 32;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + a.slice_bytes_aligned);
+  float* xchg = reinterpret_cast<float*>(full + kMaxChunks);  // [2][kMaxCluster][4]
+  float* red = xchg + 2 * kMaxCluster * 4;                     // [64]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t crank = cluster_ctarank();
+  const int C = a.C;
+  const int cid = blockIdx.x / C, ncl = gridDim.x / C;
+  const int64_t nvec_total = a.V / VE;
+  const int64_t v0 = (int64_t)crank * a.vpc;
+  int my_nvec = (int)(nvec_total - v0 < a.vpc ? nvec_total - v0 : a.vpc);
+  if (my_nvec < 0) my_nvec = 0;
+  // chunks this CTA owns (the last CTA of a cluster may own fewer vectors than a.vpc); the first
+  // `nfull` of them are complete, so their inner loops carry no bounds checks
+  const int nchunk = (my_nvec + CV - 1) / CV;
+  const int nfull = my_nvec / CV;
+  const uint32_t slice_s = smem_u32(smem_raw);
+  const uint32_t full_s = smem_u32(full);
+  const T* logits = reinterpret_cast<const T*>(a.logits);
+  T* dlogits = reinterpret_cast<T*>(a.dlogits);
+  const float log2g = FOLD ? log2f(g) : 0.f;
+  const int slice_elem0 = (int)(v0 * VE);   // first column of this CTA's slice
+
+  // issue the bulk copy of chunk k of `row` into this CTA's slice (thread 0 only)
+  auto issue_chunk = [&](int64_t row, int k) {
+    const int first = k * CV;
+    int nv = my_nvec - first;
+    if (nv <= 0) return;
+    if (nv > CV) nv = CV;
+    const uint32_t bytes = (uint32_t)nv * 16u;
+    const char* src = reinterpret_cast<const char*>(logits + row * a.rs) + (v0 + first) * 16;
+    mbar_expect_tx(full_s + 8 * k, bytes);
+    bulk_g2s(slice_s + (uint32_t)first * 16u, src, bytes, full_s + 8 * k);
+  };
+
+  int64_t row = cid;
+  if (row < a.M && tid == 0 && a.labels[row] != MDY_IGNORE_INDEX) {
+    for (int k = 0; k < nchunk; ++k) issue_chunk(row, k);
+  }
+  // rows that carried a label so far: selects the mbarrier phase and the exchange slot (two slots, so
+  // a CTA that runs ahead cannot overwrite a slot its peer is still reading: it would first have to
+  // pass the cluster barrier of the row in between)
+  uint32_t nloaded = 0;
+  bool dead = false;
+  const uint32_t my_s = slice_s + (uint32_t)tid * 16u;
+  for (; row < a.M; row += ncl) {
+    const int64_t label = a.labels[row];
+    const bool cur_valid = label != MDY_IGNORE_INDEX;
+    const int64_t nrow = row + ncl;
+    const bool next_valid = nrow < a.M && a.labels[nrow] != MDY_IGNORE_INDEX;
+    T* dst = dlogits + row * a.rs + (int64_t)slice_elem0 + (int64_t)tid * VE;
+
+    if (!cur_valid) {
+      // ignored row: nothing was loaded; zero-fill the slice and start fetching the next row
+      if (crank == 0 && tid == 0) { a.losses[row] = 0.f; a.lse[row] = 0.f; }
+      if (tid == 0 && next_valid) {
+        for (int k = 0; k < nchunk; ++k) issue_chunk(nrow, k);
+      }
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int v = tid; v < my_nvec; v += NT) st_stream(dst + (int64_t)(v - tid) * VE, z);
+      continue;
+    }
+
+    // ---- sweep 1: (max, sum-exp) of the slice as its chunks land ----
+    const uint32_t parity = nloaded & 1u;
+    float m = -INFINITY, s0 = 0.f, s1 = 0.f;
+    for (int k = 0; k < nfull; ++k) {
+      mbar_wait(full_s + 8 * k, parity, dead);
+      uint4 q[VPC];
+#pragma unroll
+      for (int j = 0; j < VPC; ++j) q[j] = lds128(my_s + (uint32_t)(k * CV + j * NT) * 16u);
+      stats_chunk<T, VPC>(q, m, s0, s1);
+    }
+    if (nfull < nchunk) {
+      mbar_wait(full_s + 8 * nfull, parity, dead);
+      uint4 q[VPC];
+#pragma unroll
+      for (int j = 0; j < VPC; ++j) {
+        const int vb = nfull * CV + j * NT;
+        q[j] = vb + tid < my_nvec ? lds128(my_s + (uint32_t)vb * 16u) : neg_inf_vec<T>();
+      }
+      stats_chunk<T, VPC>(q, m, s0, s1);
+    }
+    float s = s0 + s1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const float os = __shfl_xor_sync(0xffffffffu, s, o);
+      merge_nb(m, s, om, os);
+    }
+    if (lane == 0) { red[warp] = m; red[32 + warp] = s; }
+    __syncthreads();
+    int loc = -1;  // label position inside this CTA's slice, in elements
+    if (label >= 0 && label < a.V) {
+      const int64_t l = label - slice_elem0;
+      if (l >= 0 && l < (int64_t)my_nvec * VE) loc = (int)l;
+    }
+    if (warp == 0) {
+      m = lane < NW ? red[lane] : -INFINITY;
+      s = lane < NW ? red[32 + lane] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, m, o);
+        const float os = __shfl_xor_sync(0xffffffffu, s, o);
+        merge_nb(m, s, om, os);
+      }
+      if (lane == 0) {
+        const float xl = loc >= 0 ? to_float(reinterpret_cast<const T*>(smem_raw)[loc]) : 0.f;
+        const uint32_t slot = smem_u32(xchg + ((int)(nloaded & 1u) * kMaxCluster + (int)crank) * 4);
+        for (int p = 0; p < C; ++p) {
+          st_remote_f32(slot, p, m);
+          st_remote_f32(slot + 4, p, s);
+          st_remote_f32(slot + 8, p, xl);
+        }
+      }
+    }
+    cluster_sync_all();
+    float gm = -INFINITY, gs = 0.f, xl = 0.f;
+    {
+      const float* x = xchg + (int)(nloaded & 1u) * kMaxCluster * 4;
+      for (int p = 0; p < C; ++p) {
+        merge_nb(gm, gs, x[p * 4], x[p * 4 + 1]);
+        xl += x[p * 4 + 2];
+      }
+    }
+    const float lse = gm + logf(gs);
+    if (crank == 0 && tid == 0) {
+      a.losses[row] = (label >= 0 && label < a.V) ? lse - xl : 0.f;
+      a.lse[row] = lse;
+    }
+    ++nloaded;
+
+    // ---- sweep 2: gradient from the staged slice; refill each chunk as soon as it is consumed ----
+    const float c2 = -lse * kLog2e + log2g;
+    for (int k = 0; k < nfull; ++k) {
+      uint4 q[VPC];
+#pragma unroll
+      for (int j = 0; j < VPC; ++j) q[j] = lds128(my_s + (uint32_t)(k * CV + j * NT) * 16u);
+      __syncthreads();  // chunk k is now in registers everywhere: its buffer may be refilled
+      if (tid == 0 && next_valid) issue_chunk(nrow, k);
+#pragma unroll
+      for (int j = 0; j < VPC; ++j) st_stream(dst + (int64_t)(k * CV + j * NT) * VE, grad_vec<T, FOLD>(q[j], c2, g));
+    }
+    if (nfull < nchunk) {
+      uint4 q[VPC];
+#pragma unroll
+      for (int j = 0; j < VPC; ++j) {
+        const int vb = nfull * CV + j * NT;
+        q[j] = vb + tid < my_nvec ? lds128(my_s + (uint32_t)vb * 16u) : make_uint4(0, 0, 0, 0);
+      }
+      __syncthreads();
+      if (tid == 0 && next_valid) issue_chunk(nrow, nfull);
+#pragma unroll
+      for (int j = 0; j < VPC; ++j) {
+        const int vb = nfull * CV + j * NT;
+        if (vb + tid < my_nvec) st_stream(dst + (int64_t)vb * VE, grad_vec<T, FOLD>(q[j], c2, g));
+      }
+    }
+    // the label's element is (p - 1)*g: the thread that stored its vector overwrites that one element
+    // (same thread, same address: program order keeps the later store)
+    if (loc >= 0 && ((loc / VE) % NT) == tid) {
+      const float p = fast_exp2(fmaf(xl, kLog2e, -lse * kLog2e));
+      dlogits[row * a.rs + slice_elem0 + loc] = from_float<T>((p - 1.f) * g);
+    }
+  }
+}
+
+template <typename T, int NT, int VPC>
+__global__ void __launch_bounds__(NT, (NT <= 512 ? 3 : 1)) ce_cluster_kernel(ClusterArgs a) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  const uint32_t full_s = smem_u32(smem_raw + a.slice_bytes_aligned);
+  if (threadIdx.x == 0) {
+    for (int k = 0; k < kMaxChunks; ++k) mbar_init(full_s + 8 * k, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // every CTA of the cluster must be running before anyone writes into a peer's shared memory
+  cluster_sync_all();
+  const float g = a.ghost * (a.gdev ? *a.gdev : 1.f);
+  if (g > 0.f && g < INFINITY) cluster_rows<T, NT, VPC, true>(a, smem_raw, g);
+  else cluster_rows<T, NT, VPC, false>(a, smem_raw, g);
+}
+
+inline int cluster_slice_limit() {
+  int kb = tunable(MDY_TUNE_CE_CLUSTER_SLICE_KB);
+  if (kb < 8 || kb > 220) kb = 200;
+  return kb * 1024;
+}
+
+template <typename T, int NT, int VPC>
+int launch_cluster_nt(ClusterArgs a, cudaStream_t st) {
+  constexpr int VE = VecInfo<T>::kElems;
+  const int64_t row_bytes = a.V * (int64_t)sizeof(T);
+  const int64_t nvec = a.V / VE;
+  int C = (int)ceil_div(row_bytes, cluster_slice_limit());
+  if (C > kMaxCluster) {
+    // rows too long for 8 small slices: grow the slice up to what one CTA per SM can hold
+    C = kMaxCluster;
+    if (ceil_div(row_bytes, C) > 200 * 1024) return MDY_ERR_UNSUPPORTED;
+  }
+  const int64_t vpc = ceil_div(nvec, C);
+  if ((int64_t)(C - 1) * vpc >= nvec) return MDY_ERR_UNSUPPORTED;  // a CTA would own nothing
+  a.C = C;
+  a.vpc = (int)vpc;
+  if (ceil_div(vpc, NT * VPC) > kMaxChunks) return MDY_ERR_UNSUPPORTED;
+  a.slice_bytes_aligned = (int)((vpc * 16 + 127) / 128 * 128);
+  const size_t smem = (size_t)a.slice_bytes_aligned + kMaxChunks * 8 + 2 * kMaxCluster * 4 * 4 + 64 * 4;
+
+  auto kern = ce_cluster_kernel<T, NT, VPC>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = C; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(NT, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(C, 1, 1);
+  // co-resident clusters for this (device, kernel, cluster size, shared memory) — queried once and reused
+  static thread_local int c_dev = -1, c_C = 0, c_max = 0;
+  static thread_local size_t c_smem = 0;
+  int dev = 0;
+  (void)cudaGetDevice(&dev);
+  int max_clusters = 0;
+  if (dev == c_dev && C == c_C && smem == c_smem) {
+    max_clusters = c_max;
+  } else {
+    e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+    if (e != cudaSuccess || max_clusters < 1) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
+    c_dev = dev; c_C = C; c_smem = smem; c_max = max_clusters;
+  }
+  int64_t ncl = a.M < max_clusters ? a.M : max_clusters;
+  cfg.gridDim = dim3((unsigned)(ncl * C), 1, 1);
+  e = cudaLaunchKernelEx(&cfg, kern, a);
+  if (e != cudaSuccess) return (int)e;
+  return finish_launch(1);
+}
+
+template <typename T>
+int launch_cluster(const ClusterArgs& a, cudaStream_t st) {
+  constexpr int VE = VecInfo<T>::kElems;
+  if (a.V % VE != 0 || a.rs % VE != 0 || !aligned16(a.logits) || !aligned16(a.dlogits)) return MDY_ERR_UNSUPPORTED;
+  if (a.V >= ((int64_t)1 << 27)) return MDY_ERR_UNSUPPORTED;
+  const int nt = tunable(MDY_TUNE_CE_CLUSTER_THREADS);
+  const int vpc = tunable(MDY_TUNE_CE_CLUSTER_VPC);
+  // default (measured best at V = 128256, bf16): one 1024-thread CTA per SM, 64 KB chunks
+  if (nt == 512) {
+    if (vpc == 1) return launch_cluster_nt<T, 512, 1>(a, st);
+    if (vpc == 4) return launch_cluster_nt<T, 512, 4>(a, st);
+    return launch_cluster_nt<T, 512, 2>(a, st);
+  }
+  if (vpc == 1) return launch_cluster_nt<T, 1024, 1>(a, st);
+  if (vpc == 2) return launch_cluster_nt<T, 1024, 2>(a, st);
+  return launch_cluster_nt<T, 1024, 4>(a, st);
+}
+
+}  // namespace
+
+int ce_fused_cluster(const void* logits, void* dlogits, const int64_t* labels, float* losses, float* lse,
+                     const float* gdev, float ghost, int64_t M, int64_t V, int64_t rs, int dtype,
+                     cudaStream_t st) {
+  ClusterArgs a;
+  a.logits = logits; a.dlogits = dlogits; a.labels = labels; a.losses = losses; a.lse = lse;
+  a.gdev = gdev; a.ghost = ghost; a.M = (int)M; a.V = V; a.rs = rs;
+  a.C = 0; a.vpc = 0; a.slice_bytes_aligned = 0;
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    return launch_cluster<T>(a, st);
+  });
 }
 
 }  // namespace mdy
+
+extern "C" int mdy_last_device_error(int clear) {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, mdy::g_dev_error, sizeof(int)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -1;
+  }
+  if (clear && v != 0) {
+    const int z = 0;
+    (void)cudaMemcpyToSymbol(mdy::g_dev_error, &z, sizeof(int));
+  }
+  return v;
+}

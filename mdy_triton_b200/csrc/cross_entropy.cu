@@ -16,12 +16,13 @@ namespace {
 constexpr int kU = 4;  // 16-byte loads in flight per thread per sweep
 
 __device__ __forceinline__ void stat_merge(float& m, float& s, float om, float os) {
-  // (m, s) <- merge of two (max, sum of exp(x - max)) pairs; -inf maxima carry s == 0.
-  const float nm = fmaxf(m, om);
-  const float a = (m == -INFINITY) ? 0.f : s * fast_exp2((m - nm) * kLog2e);
-  const float b = (om == -INFINITY) ? 0.f : os * fast_exp2((om - nm) * kLog2e);
-  m = nm;
-  s = a + b;
+  // (m, s) <- merge of two (max, sum of exp(x - max)) pairs with ONE exp; -inf maxima carry s == 0.
+  if (om > m) {
+    s = ((m == -INFINITY) ? 0.f : s * fast_exp2((m - om) * kLog2e)) + os;
+    m = om;
+  } else if (om != -INFINITY) {
+    s += os * fast_exp2((om - m) * kLog2e);
+  }
 }
 
 template <int VE>
@@ -38,7 +39,7 @@ __device__ __forceinline__ void stat_update(float& m, float& s, const float* f) 
   for (int e = 0; e < VE; ++e) s += fast_exp2(fmaf(f[e], kLog2e, nm2));
 }
 
-// Block-wide (max, sum-exp) of x[0, V).  Result valid in every thread.  sm must hold 64 floats.
+// Block-wide (max, sum-exp) of x[0, V).  Result valid in every thread.  sm must hold 66 floats.
 template <typename T>
 __device__ __forceinline__ void row_stats(const T* x, int64_t V, bool vec_ok, float& m_out, float& s_out,
                                           float* sm) {
@@ -74,13 +75,25 @@ __device__ __forceinline__ void row_stats(const T* x, int64_t V, bool vec_ok, fl
     const float os = __shfl_xor_sync(0xffffffffu, s, o);
     stat_merge(m, s, om, os);
   }
+  // across warps: warp 0 merges the per-warp pairs (one per lane) and broadcasts through shared memory,
+  // so the exp work of the merge is paid by 32 threads, not by the whole CTA
   const int warp = tid >> 5, lane = tid & 31, nwarp = (BT + 31) >> 5;
   if (lane == 0) { sm[warp] = m; sm[32 + warp] = s; }
   __syncthreads();
-  float fm = sm[0], fs = sm[32];
-  for (int k = 1; k < nwarp; ++k) stat_merge(fm, fs, sm[k], sm[32 + k]);
-  m_out = fm;
-  s_out = fs;
+  if (warp == 0) {
+    m = lane < nwarp ? sm[lane] : -INFINITY;
+    s = lane < nwarp ? sm[32 + lane] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const float os = __shfl_xor_sync(0xffffffffu, s, o);
+      stat_merge(m, s, om, os);
+    }
+    if (lane == 0) { sm[64] = m; sm[65] = s; }
+  }
+  __syncthreads();
+  m_out = sm[64];
+  s_out = sm[65];
 }
 
 // dx[c] = (exp(x[c] - lse) - [c == loc]) * g for c in [0, V).  x may alias dx.
@@ -145,7 +158,7 @@ __global__ void __launch_bounds__(1024)
 ce_fwd_kernel(const T* __restrict__ logits, const int64_t* __restrict__ labels, float* __restrict__ losses,
               float* __restrict__ lse_out, int64_t V, int64_t rs, int64_t vocab_start, int split,
               int vec_ok) {
-  __shared__ float sm[64];
+  __shared__ float sm[66];
   const int64_t row = blockIdx.x;
   const int64_t label = labels[row];
   if (label == MDY_IGNORE_INDEX) {
@@ -191,7 +204,7 @@ __global__ void __launch_bounds__(1024)
 ce_fused_kernel(const T* logits, T* dlogits, const int64_t* __restrict__ labels,
                 float* __restrict__ losses, float* __restrict__ lse_out,
                 const float* __restrict__ gdev, float ghost, int64_t V, int64_t rs, int vec_ok) {
-  __shared__ float sm[64];
+  __shared__ float sm[66];
   const int64_t row = blockIdx.x;
   const int64_t label = labels[row];
   T* dx = dlogits + row * rs;

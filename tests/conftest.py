@@ -47,16 +47,17 @@ REL = {torch.bfloat16: 1e-2, torch.float16: 1e-2, torch.float32: 1e-4}
 LOSS_TOL = 1e-4
 
 
-def assert_close(actual, expected, rel, what=""):
-    """|a - b| <= rel * (|b| + mean|b|) elementwise: relative error bounded by `rel`, with an absolute
-    floor of `rel` times the tensor's typical magnitude for entries that cancel to ~0."""
+def assert_close(actual, expected, rel, what="", atol=0.0):
+    """|a - b| <= rel * (|b| + mean|b|) + atol elementwise: relative error bounded by `rel`, with an
+    absolute floor of `rel` times the tensor's typical magnitude for entries that cancel to ~0.  `atol`
+    is for outputs whose storage format underflows (float16 gradients below its subnormal step)."""
     a = actual.detach().float().cpu()
     b = expected.detach().float().cpu()
     assert a.shape == b.shape, f"{what}: shape {tuple(a.shape)} vs {tuple(b.shape)}"
     assert torch.isfinite(a).all(), f"{what}: non-finite values"
     scale = b.abs().mean()
     err = (a - b).abs()
-    tol = rel * (b.abs() + scale) + 1e-30
+    tol = rel * (b.abs() + scale) + 1e-30 + atol
     bad = err > tol
     if bad.any():
         i = torch.argmax(err / tol)

@@ -310,8 +310,19 @@ def test_swiglu_linearity_full_size():
 
 
 # ---------------------------------------------------------------------------------------- cross-entropy
+@pytest.fixture(params=["cluster", "row"], autouse=False)
+def fused_impl(request):
+    """Run a test under both one-pass implementations: the cluster/shared-memory kernel (default where
+    the shape fits) and the row-per-CTA kernel it falls back to."""
+    _C.set_tunable(_C.TUNE_CE_FUSED_IMPL, 1 if request.param == "row" else 0)
+    yield request.param
+    _C.set_tunable(_C.TUNE_CE_FUSED_IMPL, 0)
+    torch.cuda.synchronize()
+    assert _C.lib().mdy_last_device_error(1) == 0, "a bounded device-side wait expired"
+
+
 @pytest.mark.parametrize("c", golden_cases("cross_entropy.pt"))
-def test_ce_golden(c):
+def test_ce_golden(c, fused_impl):
     lg, lb = c["logits"], c["labels"].to(DEV)
     r = REL[lg.dtype]
     x = leaf(lg)
@@ -352,19 +363,21 @@ def test_ce_golden(c):
     (1, 8192, 10.0, 0.0, torch.bfloat16),
     (7, 1000, 1.0, 1.0, torch.bfloat16),        # every row ignored
 ])
-def test_ce_vs_oracle(m, v, sigma, frac, dt):
+def test_ce_vs_oracle(m, v, sigma, frac, dt, fused_impl):
     gen = g(m + v)
     lg = (torch.randn(m, v, generator=gen) * sigma).to(dt)
     lb = torch.randint(0, v, (m,), generator=gen)
     lb[torch.rand(m, generator=gen) < frac] = -100
     dl = torch.randn(m, generator=gen)
     r = REL[dt]
+    # float16 gradients of tiny probabilities underflow: allow one subnormal step of the storage format
+    atol = 2.0 ** -24 if dt == torch.float16 else 0.0
     lo, lse_o = E.ce_rows(lg, lb)
     # two-phase path
     x = leaf(lg)
     losses = _FastCrossEntropyLoss.apply(x, lb.to(DEV), False); losses.backward(dl.to(DEV))
     assert torch.allclose(losses.cpu(), lo, rtol=LOSS_TOL, atol=LOSS_TOL)
-    assert_close(x.grad, E.ce_grad(lg, lb, lse_o, dl), r, "dlogits")
+    assert_close(x.grad, E.ce_grad(lg, lb, lse_o, dl), r, "dlogits", atol)
     # one-pass path, in place and not
     n = int((lb != -100).sum())
     for inplace in (False, True):
@@ -374,14 +387,14 @@ def test_ce_vs_oracle(m, v, sigma, frac, dt):
             assert torch.isnan(loss)  # 0/0, as in the reference
             continue
         loss_close(loss, E.ce_scalar(lg, lb))
-        assert_close(x.grad, E.ce_grad(lg, lb, lse_o, torch.tensor(1.0 / n)), r, f"fused dlogits inplace={inplace}")
+        assert_close(x.grad, E.ce_grad(lg, lb, lse_o, torch.tensor(1.0 / n)), r, f"fused dlogits inplace={inplace}", atol)
         if inplace:
             assert torch.equal(xin.detach(), x.grad)
     if n:
         loss_close(E.hf_cross_entropy(lg, lb), E.ce_scalar(lg, lb))
 
 
-def test_ce_upstream_gradient_scaling():
+def test_ce_upstream_gradient_scaling(fused_impl):
     """loss * 0.25 (gradient accumulation) must scale the gradient the forward already wrote."""
     gen = g(9)
     lg = (torch.randn(32, 4096, generator=gen) * 2).to(torch.bfloat16); lb = torch.randint(0, 4096, (32,), generator=gen)
@@ -404,7 +417,7 @@ def test_ce_out_of_range_label_and_neg_inf_logits():
     assert torch.isfinite(x.grad).all()
 
 
-def test_ce_properties_full_size():
+def test_ce_properties_full_size(fused_impl):
     """Llama-3 shape slice at full vocabulary, 8192 rows (2.1 GB of logits): valid rows of dlogits sum to
     ~0 (softmax minus one-hot), ignored rows are exactly 0, the label entry is the only negative one,
     and the one-pass kernel agrees with the two-phase kernels."""
