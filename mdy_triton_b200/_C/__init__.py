@@ -27,6 +27,7 @@ TUNE_ROPE_THREADS = 5
 TUNE_CE_CLUSTER_SLICE_KB = 6
 TUNE_CE_CLUSTER_THREADS = 7
 TUNE_CE_CLUSTER_VPC = 8
+TUNE_CE_REG_SHAPE = 9
 
 _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 

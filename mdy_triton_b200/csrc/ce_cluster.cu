@@ -71,25 +71,27 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t
                "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
-__device__ __forceinline__ void st_remote_f32(uint32_t local_addr, uint32_t rank, float v) {
-  uint32_t ra;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// 16 bytes into CTA `rank`'s shared memory at the same offset as `local_addr`, completing 16 tx bytes
+// on that CTA's mbarrier at the same offset as `local_bar`: data and signal travel together, so the
+// receiver needs no cluster-wide barrier or fence (a release fence would also wait for the sender's
+// outstanding gradient stores to global memory).
+__device__ __forceinline__ void st_async_v4(uint32_t local_addr, uint32_t local_bar, uint32_t rank, float a, float b,
+                                            float c, float d) {
+  uint32_t ra, rb;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_addr), "r"(rank));
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rb) : "r"(local_bar), "r"(rank));
+  asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(ra),
+               "f"(a), "f"(b), "f"(c), "f"(d), "r"(rb)
+               : "memory");
+}
+
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
   return v;
-}
-
-// (m, s) <- merge with (om, os): one exp per merge; -inf maxima carry s == 0
-__device__ __forceinline__ void merge1(float& m, float& s, float om, float os) {
-  if (om > m) {
-    s = ((m == -INFINITY) ? 0.f : s * fast_exp2((m - om) * kLog2e)) + os;
-    m = om;
-  } else if (om != -INFINITY) {
-    s += os * fast_exp2((om - m) * kLog2e);
-  }
 }
 
 // A 16-byte vector whose every element is -inf: padding that changes neither a max nor a sum of exps.
@@ -184,8 +186,8 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
   constexpr int CV = NT * VPC;            // vectors per chunk
   constexpr int NW = NT / 32;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + a.slice_bytes_aligned);
-  float* xchg = reinterpret_cast<float*>(full + kMaxChunks);  // [2][kMaxCluster][4]
-  float* red = xchg + 2 * kMaxCluster * 4;                     // [64]
+  float* xchg = reinterpret_cast<float*>(full + kMaxChunks + 2);  // [2][kMaxCluster][4]; full[] is followed by xbar[2]
+  float* red = xchg + 2 * kMaxCluster * 4;                         // [64]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const uint32_t crank = cluster_ctarank();
@@ -290,16 +292,18 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
         merge_nb(m, s, om, os);
       }
       if (lane == 0) {
+        // (max, sum, label logit) to every CTA of the cluster, itself included: 16 bytes that complete
+        // 16 tx bytes on the receiver's exchange barrier (no cluster-wide barrier or fence per row)
         const float xl = loc >= 0 ? to_float(reinterpret_cast<const T*>(smem_raw)[loc]) : 0.f;
+        const uint32_t xb = full_s + 8 * (kMaxChunks + (nloaded & 1u));
         const uint32_t slot = smem_u32(xchg + ((int)(nloaded & 1u) * kMaxCluster + (int)crank) * 4);
-        for (int p = 0; p < C; ++p) {
-          st_remote_f32(slot, p, m);
-          st_remote_f32(slot + 4, p, s);
-          st_remote_f32(slot + 8, p, xl);
-        }
+        mbar_expect_tx(xb, (uint32_t)C * 16u);
+        for (int p = 0; p < C; ++p) st_async_v4(slot, xb, (uint32_t)p, m, s, xl, 0.f);
       }
     }
-    cluster_sync_all();
+    // two exchange slots suffice: a peer cannot send for row n+2 before it has this CTA's message for
+    // row n+1, which leaves only after the reads of row n below
+    mbar_wait(full_s + 8 * (kMaxChunks + (nloaded & 1u)), (nloaded >> 1) & 1u, dead);
     float gm = -INFINITY, gs = 0.f, xl = 0.f;
     {
       const float* x = xchg + (int)(nloaded & 1u) * kMaxCluster * 4;
@@ -355,7 +359,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 3 : 1)) ce_cluster_kernel(Clu
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t full_s = smem_u32(smem_raw + a.slice_bytes_aligned);
   if (threadIdx.x == 0) {
-    for (int k = 0; k < kMaxChunks; ++k) mbar_init(full_s + 8 * k, 1);
+    for (int k = 0; k < kMaxChunks + 2; ++k) mbar_init(full_s + 8 * k, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
@@ -389,7 +393,7 @@ int launch_cluster_nt(ClusterArgs a, cudaStream_t st) {
   a.vpc = (int)vpc;
   if (ceil_div(vpc, NT * VPC) > kMaxChunks) return MDY_ERR_UNSUPPORTED;
   a.slice_bytes_aligned = (int)((vpc * 16 + 127) / 128 * 128);
-  const size_t smem = (size_t)a.slice_bytes_aligned + kMaxChunks * 8 + 2 * kMaxCluster * 4 * 4 + 64 * 4;
+  const size_t smem = (size_t)a.slice_bytes_aligned + (kMaxChunks + 2) * 8 + 2 * kMaxCluster * 4 * 4 + 64 * 4;
 
   auto kern = ce_cluster_kernel<T, NT, VPC>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -431,15 +435,308 @@ int launch_cluster(const ClusterArgs& a, cudaStream_t st) {
   if (a.V >= ((int64_t)1 << 27)) return MDY_ERR_UNSUPPORTED;
   const int nt = tunable(MDY_TUNE_CE_CLUSTER_THREADS);
   const int vpc = tunable(MDY_TUNE_CE_CLUSTER_VPC);
-  // default (measured best at V = 128256, bf16): one 1024-thread CTA per SM, 64 KB chunks
+  // default (measured best at V = 128256, bf16): one 1024-thread CTA per SM, 32 KB chunks
   if (nt == 512) {
     if (vpc == 1) return launch_cluster_nt<T, 512, 1>(a, st);
     if (vpc == 4) return launch_cluster_nt<T, 512, 4>(a, st);
     return launch_cluster_nt<T, 512, 2>(a, st);
   }
   if (vpc == 1) return launch_cluster_nt<T, 1024, 1>(a, st);
-  if (vpc == 2) return launch_cluster_nt<T, 1024, 2>(a, st);
-  return launch_cluster_nt<T, 1024, 4>(a, st);
+  if (vpc == 4) return launch_cluster_nt<T, 1024, 4>(a, st);
+  return launch_cluster_nt<T, 1024, 2>(a, st);
+}
+
+
+// =================================================================================================
+// Register-resident variant.
+//
+// Each thread keeps the exponentials of its NVEC vectors of the row in float registers between the
+// two sweeps, so every logit costs ONE exp: sweep 1 stores e = exp2(x*log2e - ref*log2e) (ref = the
+// thread's running max when the chunk was processed), sweep 2 multiplies by one per-chunk factor
+// exp2((ref - lse)*log2e) * g, packs and stores.  Shared memory only holds a ring of bulk-copy
+// buffers two rows deep (one "full" and one "empty" mbarrier per buffer): a buffer is released as
+// soon as its 16 bytes per thread are in registers, and thread 0 refills it with the same chunk of
+// the row two positions ahead, so loads run a whole row ahead of the math.
+// =================================================================================================
+template <typename T, int NT, int NVEC>
+__global__ void __launch_bounds__(NT, (NT * NVEC <= 2048 ? 2 : 1)) ce_regrow_kernel(ClusterArgs a) {
+  constexpr int VE = VecInfo<T>::kElems;
+  constexpr int NW = NT / 32;
+  constexpr int NSLOT = 2 * NVEC;
+  constexpr uint32_t SLOT_BYTES = NT * 16;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)NSLOT * SLOT_BYTES);  // full[NSLOT], empty[NSLOT], xbar[2]
+  float* xchg = reinterpret_cast<float*>(bars + 2 * NSLOT + 2);                         // [2][kMaxCluster][4]
+  float* red = xchg + 2 * kMaxCluster * 4;                                               // [72]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t crank = cluster_ctarank();
+  const int C = a.C;
+  const int cid = blockIdx.x / C, ncl = gridDim.x / C;
+  const int64_t nvec_total = a.V / VE;
+  const int64_t v0 = (int64_t)crank * a.vpc;
+  int my_nvec = (int)(nvec_total - v0 < a.vpc ? nvec_total - v0 : a.vpc);
+  if (my_nvec < 0) my_nvec = 0;
+  const int nj = (my_nvec + NT - 1) / NT;   // chunks of this CTA's slice, <= NVEC
+  const uint32_t ring_s = smem_u32(smem_raw);
+  const uint32_t full_s = smem_u32(bars);
+  const uint32_t empty_s = full_s + 8 * NSLOT;
+  const uint32_t xbar_s = empty_s + 8 * NSLOT;   // exchange barriers, one per parity of the row count
+  const T* logits = reinterpret_cast<const T*>(a.logits);
+  T* dlogits = reinterpret_cast<T*>(a.dlogits);
+  const int slice_elem0 = (int)(v0 * VE);
+
+  if (tid == 0) {
+    for (int k = 0; k < NSLOT; ++k) {
+      mbar_init(full_s + 8 * k, 1);
+      mbar_init(empty_s + 8 * k, NW);
+    }
+    mbar_init(xbar_s, 1);
+    mbar_init(xbar_s + 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  cluster_sync_all();  // all CTAs of the cluster run before anyone writes a peer's shared memory
+  const float g = a.ghost * (a.gdev ? *a.gdev : 1.f);
+
+  // ---- producer state, used by thread 0 only ----
+  int64_t prow = cid;  // next row of this cluster's sequence that has not been looked at for issue
+  auto next_labelled_row = [&]() -> int64_t {
+    while (prow < a.M && a.labels[prow] == MDY_IGNORE_INDEX) prow += ncl;
+    const int64_t r = prow;
+    if (prow < a.M) prow += ncl;
+    return r;  // >= M: none left
+  };
+  // bulk copy of chunk j of `row` into ring position `pos` (position parity selects the buffer group)
+  auto issue = [&](int64_t row, uint32_t pos, int j) {
+    const int first = j * NT;
+    int nv = my_nvec - first;
+    if (nv <= 0) return;
+    if (nv > NT) nv = NT;
+    const uint32_t slot = (pos & 1u) * NVEC + (uint32_t)j;
+    const char* src = reinterpret_cast<const char*>(logits + row * a.rs) + (v0 + first) * 16;
+    mbar_expect_tx(full_s + 8 * slot, (uint32_t)nv * 16u);
+    bulk_g2s(ring_s + slot * SLOT_BYTES, src, (uint32_t)nv * 16u, full_s + 8 * slot);
+  };
+  if (tid == 0) {
+    for (uint32_t pos = 0; pos < 2; ++pos) {
+      const int64_t r = next_labelled_row();
+      if (r < a.M)
+        for (int j = 0; j < nj; ++j) issue(r, pos, j);
+    }
+  }
+
+  uint32_t n_cons = 0;  // labelled rows consumed so far == ring position of the current one
+  bool dead = false;
+#ifdef MDY_CE_TIMING
+  long long tacc[6] = {0, 0, 0, 0, 0, 0};
+#define MDY_TICK(i) { const long long t_ = clock64(); tacc[i] += t_ - tlast; tlast = t_; }
+  long long tlast = clock64();
+#else
+#define MDY_TICK(i)
+#endif
+  for (int64_t row = cid; row < a.M; row += ncl) {
+    const int64_t label = a.labels[row];
+    T* dst = dlogits + row * a.rs + (int64_t)slice_elem0 + (int64_t)tid * VE;
+    MDY_TICK(0)
+    if (label == MDY_IGNORE_INDEX) {
+      if (crank == 0 && tid == 0) { a.losses[row] = 0.f; a.lse[row] = 0.f; }
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int v = tid; v < my_nvec; v += NT) st_stream(dst + (int64_t)(v - tid) * VE, z);
+      continue;
+    }
+    // the row that will take this row's buffers (ring position n_cons + 2)
+    int64_t r2 = a.M;
+    if (tid == 0) r2 = next_labelled_row();
+    const uint32_t slotbase = (n_cons & 1u) * NVEC;
+    const uint32_t par = (n_cons >> 1) & 1u;
+    int loc = -1;
+    if (label >= 0 && label < a.V) {
+      const int64_t l = label - slice_elem0;
+      if (l >= 0 && l < (int64_t)my_nvec * VE) loc = (int)l;
+    }
+    const int loc_vec = loc >= 0 ? loc / VE : -1;
+
+    // ---- sweep 1 ----
+    float e[NVEC][VE];
+    float ref[NVEC];
+    float m = -INFINITY, s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NVEC; ++j) {
+      if (j < nj) {
+        const uint32_t slot = slotbase + (uint32_t)j;
+        mbar_wait(full_s + 8 * slot, par, dead);
+        const int v = j * NT + tid;
+        const uint4 q = v < my_nvec ? lds128(ring_s + slot * SLOT_BYTES + (uint32_t)tid * 16u) : neg_inf_vec<T>();
+        float f[VE];
+        unpack<T>(q, f);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_s + 8 * slot);   // this warp holds its part of the buffer in registers
+        if (tid == 0 && r2 < a.M && j >= 1) {             // refill the buffer released one step ago
+          mbar_wait(empty_s + 8 * (slot - 1), par, dead);
+          issue(r2, n_cons + 2, j - 1);
+        }
+        const float vm = vec_max<T>(q);
+        if (vm > m) {
+          const float r = fast_exp2((fmaxf(m, -1e37f) - vm) * kLog2e);
+          s0 *= r; s1 *= r;
+          m = vm;
+        }
+        ref[j] = m;
+        const float nm2 = -fmaxf(m, -1e37f) * kLog2e;
+        if (v == loc_vec) {  // the label's logit, for the loss
+          float xl = 0.f;
+#pragma unroll
+          for (int k = 0; k < VE; ++k)
+            if (k == loc - loc_vec * VE) xl = f[k];
+          red[70] = xl;
+        }
+#pragma unroll
+        for (int k = 0; k < VE; k += 2) {
+          e[j][k] = fast_exp2(fmaf(f[k], kLog2e, nm2));
+          e[j][k + 1] = fast_exp2(fmaf(f[k + 1], kLog2e, nm2));
+          s0 += e[j][k];
+          s1 += e[j][k + 1];
+        }
+      }
+    }
+    MDY_TICK(1)
+    if (tid == 0 && r2 < a.M) {
+      mbar_wait(empty_s + 8 * (slotbase + (uint32_t)nj - 1), par, dead);
+      issue(r2, n_cons + 2, nj - 1);
+    }
+    float s = s0 + s1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const float os = __shfl_xor_sync(0xffffffffu, s, o);
+      merge_nb(m, s, om, os);
+    }
+    // m, s now hold the warp's pair; keep the thread's own history in ref[]
+    if (lane == 0) { red[warp] = m; red[32 + warp] = s; }
+    __syncthreads();
+    MDY_TICK(2)
+    if (warp == 0) {
+      float wm = lane < NW ? red[lane] : -INFINITY;
+      float ws = lane < NW ? red[32 + lane] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, wm, o);
+        const float os = __shfl_xor_sync(0xffffffffu, ws, o);
+        merge_nb(wm, ws, om, os);
+      }
+      if (lane == 0) {
+        // send this CTA's (max, sum, label logit) to every CTA of the cluster, itself included; each
+        // receiver's barrier completes when all C messages (16 bytes each) have landed
+        const float xl = loc >= 0 ? red[70] : 0.f;
+        const uint32_t xb = xbar_s + 8 * (n_cons & 1u);
+        const uint32_t slotx = smem_u32(xchg + ((int)(n_cons & 1u) * kMaxCluster + (int)crank) * 4);
+        mbar_expect_tx(xb, (uint32_t)C * 16u);
+        for (int p = 0; p < C; ++p) st_async_v4(slotx, xb, (uint32_t)p, wm, ws, xl, 0.f);
+      }
+    }
+    // Two exchange slots suffice: a peer needs this CTA's message for row n+1 before it can send
+    // anything for row n+2, and that message is sent only after the reads of row n below.
+    mbar_wait(xbar_s + 8 * (n_cons & 1u), par, dead);
+    MDY_TICK(3)
+    float gm = -INFINITY, gs = 0.f, xl = 0.f;
+    {
+      const float* x = xchg + (int)(n_cons & 1u) * kMaxCluster * 4;
+      for (int p = 0; p < C; ++p) {
+        merge_nb(gm, gs, x[p * 4], x[p * 4 + 1]);
+        xl += x[p * 4 + 2];
+      }
+    }
+    const float lse = gm + logf(gs);
+    if (crank == 0 && tid == 0) {
+      a.losses[row] = (label >= 0 && label < a.V) ? lse - xl : 0.f;
+      a.lse[row] = lse;
+    }
+
+    // ---- sweep 2: from registers ----
+#pragma unroll
+    for (int j = 0; j < NVEC; ++j) {
+      if (j < nj) {
+        const int v = j * NT + tid;
+        if (v < my_nvec) {
+          const float fac = fast_exp2((ref[j] - lse) * kLog2e) * g;
+          float o[VE];
+#pragma unroll
+          for (int k = 0; k < VE; ++k) o[k] = e[j][k] * fac;
+          st_stream(dst + (int64_t)(j * NT) * VE, pack<T>(o));
+        }
+      }
+    }
+    if (loc >= 0 && (loc_vec % NT) == tid) {
+      const float p = fast_exp2((xl - lse) * kLog2e);
+      dlogits[row * a.rs + slice_elem0 + loc] = from_float<T>((p - 1.f) * g);
+    }
+    ++n_cons;
+    MDY_TICK(4)
+  }
+#ifdef MDY_CE_TIMING
+  if (blockIdx.x < 8 && (tid == 0 || tid == 40 || tid == NT - 1)) {
+    float* o = a.lse + a.M + (blockIdx.x * 3 + (tid == 0 ? 0 : tid == 40 ? 1 : 2)) * 8;
+    for (int i = 0; i < 5; ++i) o[i] = (float)tacc[i];
+    o[5] = (float)n_cons;
+  }
+#endif
+}
+
+template <typename T, int NT, int NVEC>
+int launch_regrow_nt(ClusterArgs a, cudaStream_t st) {
+  constexpr int VE = VecInfo<T>::kElems;
+  const int64_t nvec = a.V / VE;
+  const int C = (int)ceil_div(nvec, (int64_t)NT * NVEC);
+  if (C > kMaxCluster) return MDY_ERR_UNSUPPORTED;
+  const int64_t vpc = ceil_div(nvec, C);
+  if ((int64_t)(C - 1) * vpc >= nvec) return MDY_ERR_UNSUPPORTED;
+  a.C = C;
+  a.vpc = (int)vpc;
+  a.slice_bytes_aligned = 0;
+  const size_t smem = (size_t)2 * NVEC * NT * 16 + (size_t)(4 * NVEC + 2) * 8 + 2 * kMaxCluster * 4 * 4 + 72 * 4;
+  auto kern = ce_regrow_kernel<T, NT, NVEC>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = C; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(NT, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(C, 1, 1);
+  static thread_local int c_dev = -1, c_C = 0, c_max = 0;
+  int dev = 0;
+  (void)cudaGetDevice(&dev);
+  int max_clusters = 0;
+  if (dev == c_dev && C == c_C) {
+    max_clusters = c_max;
+  } else {
+    e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+    if (e != cudaSuccess || max_clusters < 1) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
+    c_dev = dev; c_C = C; c_max = max_clusters;
+  }
+  int64_t ncl = a.M < max_clusters ? a.M : max_clusters;
+  cfg.gridDim = dim3((unsigned)(ncl * C), 1, 1);
+  e = cudaLaunchKernelEx(&cfg, kern, a);
+  if (e != cudaSuccess) return (int)e;
+  return finish_launch(1);
+}
+
+template <typename T>
+int launch_regrow(const ClusterArgs& a, cudaStream_t st) {
+  constexpr int VE = VecInfo<T>::kElems;
+  if (a.V % VE != 0 || a.rs % VE != 0 || !aligned16(a.logits) || !aligned16(a.dlogits)) return MDY_ERR_UNSUPPORTED;
+  if (a.V >= ((int64_t)1 << 27)) return MDY_ERR_UNSUPPORTED;
+  switch (tunable(MDY_TUNE_CE_REG_SHAPE)) {
+    case 1: return launch_regrow_nt<T, 256, 8>(a, st);
+    case 2: return launch_regrow_nt<T, 512, 4>(a, st);
+    case 4: return launch_regrow_nt<T, 1024, 4>(a, st);
+    default: return launch_regrow_nt<T, 512, 8>(a, st);
+  }
 }
 
 }  // namespace
@@ -451,8 +748,13 @@ int ce_fused_cluster(const void* logits, void* dlogits, const int64_t* labels, f
   a.logits = logits; a.dlogits = dlogits; a.labels = labels; a.losses = losses; a.lse = lse;
   a.gdev = gdev; a.ghost = ghost; a.M = (int)M; a.V = V; a.rs = rs;
   a.C = 0; a.vpc = 0; a.slice_bytes_aligned = 0;
+  const int impl = tunable(MDY_TUNE_CE_FUSED_IMPL);
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
+    // The shared-memory kernel is the default: with 32 warps per SM it keeps the issue slots 60 % busy.
+    // The register-resident kernel needs one exp per logit instead of two but leaves room for only
+    // 16 warps per SM and measured slower; it stays selectable for experiments.
+    if (impl == 3) return launch_regrow<T>(a, st);
     return launch_cluster<T>(a, st);
   });
 }

@@ -310,13 +310,18 @@ def test_swiglu_linearity_full_size():
 
 
 # ---------------------------------------------------------------------------------------- cross-entropy
-@pytest.fixture(params=["cluster", "row"], autouse=False)
+@pytest.fixture(params=["reg512x8", "reg256x8", "reg512x4", "reg1024x4", "smem", "row"], autouse=False)
 def fused_impl(request):
-    """Run a test under both one-pass implementations: the cluster/shared-memory kernel (default where
-    the shape fits) and the row-per-CTA kernel it falls back to."""
-    _C.set_tunable(_C.TUNE_CE_FUSED_IMPL, 1 if request.param == "row" else 0)
+    """Run a test under every one-pass implementation: the cluster kernel that keeps the row's
+    exponentials in registers (default where the shape fits; four thread/vector shapes), the cluster
+    kernel that stages the row in shared memory, and the row-per-CTA kernel both fall back to."""
+    impl = {"row": 1, "smem": 2}.get(request.param, 3)
+    shape = {"reg512x8": 0, "reg256x8": 1, "reg512x4": 2, "reg1024x4": 4}.get(request.param, 0)
+    _C.set_tunable(_C.TUNE_CE_FUSED_IMPL, impl)
+    _C.set_tunable(_C.TUNE_CE_REG_SHAPE, shape)
     yield request.param
     _C.set_tunable(_C.TUNE_CE_FUSED_IMPL, 0)
+    _C.set_tunable(_C.TUNE_CE_REG_SHAPE, 0)
     torch.cuda.synchronize()
     assert _C.lib().mdy_last_device_error(1) == 0, "a bounded device-side wait expired"
 
