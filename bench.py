@@ -50,7 +50,7 @@ OPS = ("norm", "rope", "swiglu", "cross_entropy")
 FALLBACK_PEAK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one one-pass cross-entropy launch, from the ncu capture
 # summarised under profiles/ (None until a capture exists): bytes per row of the captured case.
-CE_TRAFFIC_BYTES_PER_ROW = None
+CE_TRAFFIC_BYTES_PER_ROW = 499036  # (1.0508 GB + 0.9933 GB) / 4096 rows at V = 128256, bf16
 
 
 def algorithmic_bytes(cfg, tokens, ignored_frac, s=2):
@@ -89,7 +89,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
-                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                          "--format=csv,noheader,nounits", "-lms", "20"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -410,7 +410,6 @@ def main():
     if rank == 0:
         sampler.start()
     total_ms, per_op_ms, launches = run_device_arm(ops, args.steps, warmup, barrier)
-    clocks = sampler.stop() if rank == 0 else None
     total_ms = max_over_ranks(total_ms)
     ms_per_step = total_ms / args.steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
@@ -425,6 +424,7 @@ def main():
         e2e = {"value": world * step_bytes / (e_ms * 1e-3) / 1e9, "unit": unit, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "ms_per_step": e_ms, "loss": loss}
 
+    clocks = sampler.stop() if rank == 0 else None  # sampled over both timed regions (device arm and e2e arm)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         gbs, dt, M, cores = run_cpu_baseline(cfg, args.cpu_tokens, 2, 1, cfg["seed"])
@@ -433,7 +433,8 @@ def main():
 
     if rank == 0:
         ce = per_op["cross_entropy"]
-        traffic = None if CE_TRAFFIC_BYTES_PER_ROW is None else CE_TRAFFIC_BYTES_PER_ROW * ops.M
+        # the capture is of the V = 128256 bf16 kernel; other vocabularies have no capture
+        traffic = CE_TRAFFIC_BYTES_PER_ROW * ops.M if (CE_TRAFFIC_BYTES_PER_ROW and cfg["vocab"] == 128256) else None
         out = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warmup,
                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
                "data": "synthetic", "config": config, "frac_of_peak": value / world / peak, "per_op": per_op,
