@@ -102,6 +102,27 @@ int mdy_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
                     int64_t M, int64_t N, int64_t dy_row_stride, int64_t x_row_stride,
                     int64_t dx_row_stride, int dtype, int w_dtype, void* stream);
 
+/* Same computation and results as mdy_rmsnorm_bwd, for callers that have no device allocator to get
+ * the dw_partial scratch from: a host runtime that hands the library fixed buffers only, or code inside
+ * a region where cudaMalloc (and torch's caching allocator, which may fall through to it) must not run.
+ * It has no counterpart in the reference, which always allocates the partials with torch
+ * (core/rmsnorm.py:80).  The partial rows live in a fixed 16 MiB array inside the library's device image
+ * (held by every GPU that loads the library until the process exits), so nothing is allocated or freed,
+ * here or in any routine this calls.
+ *   limit      mdy_rmsnorm_bwd_partial_rows(M, N, dtype) * N <= 4 * 2^20 floats (on a 148-SM B200:
+ *              N <= 14168 with 16-bit activations); larger problems return MDY_ERR_UNSUPPORTED and
+ *              launch nothing.
+ *   first call on each device resolves the array's device address (cudaGetSymbolAddress) with that
+ *              device current; make that first call outside any stream capture.
+ *   sharing    every call on a device uses the same array.  Nothing in it has to start at zero (each
+ *              call overwrites every partial it later reads), but two calls whose kernels overlap on
+ *              the GPU — different streams, or different host threads on different streams — race on
+ *              it: serialise them on one stream or with events. */
+int mdy_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd,
+                            void* dx, void* dw,
+                            int64_t M, int64_t N, int64_t dy_row_stride, int64_t x_row_stride,
+                            int64_t dx_row_stride, int dtype, int w_dtype, void* stream);
+
 /* new_res = x + res (float32 sum, stored as T); y = rmsnorm(unrounded sum) * w; rstd as above.
  * Replaces _add_rmsnorm_fwd launched at core/fused_add_norm.py:71 (kernel :6-26).
  * All of x,res,y,new_res are T [M,N] sharing `row_stride`. */

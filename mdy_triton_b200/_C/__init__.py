@@ -43,6 +43,7 @@ SIGNATURES = {
     "mdy_rmsnorm_bwd_partial_rows": (_L, [_L, _L, _I]),
     "mdy_rmsnorm_fwd": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _F, _I, _I, _P]),
     "mdy_rmsnorm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _I, _I, _P]),
+    "mdy_rmsnorm_bwd_noalloc": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _I, _I, _P]),
     "mdy_add_rmsnorm_fwd": (_I, [_P, _P, _P, _P, _P, _P, _L, _L, _L, _F, _I, _I, _P]),
     "mdy_add_rmsnorm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _I, _I, _P]),
     "mdy_rope": (_I, [_P, _P, _P, _P, _P, _P] + [_L] * 6 + [_L] * 12 + [_I, _I, _P]),

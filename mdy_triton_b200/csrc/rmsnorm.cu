@@ -8,6 +8,7 @@
 // is warp shuffles plus one shared-memory exchange (double-buffered: one __syncthreads per row).
 // Backward accumulates dw in float registers, folds the groups of a CTA through shared memory and
 // writes one float partial row per CTA; a second small kernel sums the partials and casts.
+#include <atomic>
 #include "common.cuh"
 
 namespace mdy {
@@ -463,6 +464,30 @@ inline int check_mn(int64_t M, int64_t N) {
 
 inline bool dtype_ok(int d) { return d == MDY_F32 || d == MDY_F16 || d == MDY_BF16; }
 
+// ---- scratch for mdy_rmsnorm_bwd_noalloc --------------------------------------------------------
+// Lives in the library's device image: every GPU that loads the library holds these 16 MiB until the
+// process exits.  In host code the NAME below is only a handle for the runtime, not a device address;
+// the address a kernel can use comes from cudaGetSymbolAddress, asked once per device.
+constexpr int64_t kNoAllocFloats = (int64_t)4 << 20;
+static __device__ __align__(256) float g_noalloc_partials[kNoAllocFloats];
+
+// Device address of the scratch on the current device (resolved on first use per device), or nullptr
+// with *err set.  Not an allocation: the array already exists in the loaded module.
+inline float* noalloc_scratch(cudaError_t* err) {
+  static std::atomic<float*> ptrs[64];
+  *err = cudaSuccess;
+  int dev = 0;
+  if ((*err = cudaGetDevice(&dev)) != cudaSuccess) return nullptr;
+  if (dev < 0 || dev >= 64) { *err = cudaErrorInvalidDevice; return nullptr; }
+  float* p = ptrs[dev].load(std::memory_order_acquire);
+  if (p) return p;
+  void* sym = nullptr;
+  if ((*err = cudaGetSymbolAddress(&sym, g_noalloc_partials)) != cudaSuccess) return nullptr;
+  p = static_cast<float*>(sym);
+  ptrs[dev].store(p, std::memory_order_release);
+  return p;
+}
+
 }  // namespace
 }  // namespace mdy
 
@@ -508,6 +533,30 @@ int mdy_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
     using T = decltype(tag);
     return launch_bwd<T, false>(dy, x, w, w_dtype, rstd, nullptr, dx, dw, dw_partial, M, N,
                                 dy_row_stride, x_row_stride, 0, dx_row_stride, (cudaStream_t)stream);
+  });
+}
+
+int mdy_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                            void* dw, int64_t M, int64_t N, int64_t dy_row_stride,
+                            int64_t x_row_stride, int64_t dx_row_stride, int dtype, int w_dtype,
+                            void* stream) {
+  if (int rc = check_mn(M, N)) return rc;
+  if (!dtype_ok(w_dtype) || !dtype_ok(dtype)) return MDY_ERR_DTYPE;
+  if (!dw || !w) return MDY_ERR_NULL;
+  if (M > 0 && (!dy || !x || !rstd || !dx)) return MDY_ERR_NULL;
+  if (dy_row_stride < 0 || x_row_stride < N || dx_row_stride < N) return MDY_ERR_SIZE;
+  // the partial-row scratch has a fixed size: refuse problems that would not fit
+  if (mdy_rmsnorm_bwd_partial_rows(M, N, dtype) * N > kNoAllocFloats) return MDY_ERR_UNSUPPORTED;
+  cudaError_t err;
+  float* scratch = noalloc_scratch(&err);
+  if (!scratch) {
+    (void)cudaGetLastError();
+    return err != cudaSuccess ? (int)err : MDY_ERR_ARG;
+  }
+  return dispatch_dtype(dtype, [&](auto tag) {
+    using T = decltype(tag);
+    return launch_bwd<T, false>(dy, x, w, w_dtype, rstd, nullptr, dx, dw, scratch, M, N, dy_row_stride,
+                                x_row_stride, 0, dx_row_stride, (cudaStream_t)stream);
   });
 }
 
