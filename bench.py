@@ -340,6 +340,74 @@ def run_cpu_baseline(cfg, tokens, steps, warmup, seed):
     return nbytes / dt / 1e9, dt, M, torch.get_num_threads()
 
 
+# ------------------------------------------------------------------------------------ Llama-1B train step
+def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, seq=4096):
+    """BASELINE config 4: random-init Llama-style 1B decoder (16 layers, hidden 2048, 32 q / 8 kv heads,
+    head_dim 64, FFN 8192, vocab 128256, eps 1e-5, theta 5e5), bf16 parameters with float32 master weights
+    and AdamW state, full forward+backward+optimizer step, synthetic tokens uniform in the vocabulary,
+    micro-batch 4 x 4096 per GPU, DDP gradient all-reduce over NCCL when world > 1.  Returns a dict."""
+    import torch.nn as nn
+    if patched:
+        import mdy_triton.replace_kernel  # noqa: F401  (the import is the patch)
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from mdy_triton_b200 import _C
+    cfg = LlamaConfig(hidden_size=2048, intermediate_size=8192, num_hidden_layers=16, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=64, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0,
+                      max_position_embeddings=seq, tie_word_embeddings=False, attn_implementation="sdpa")
+    torch.manual_seed(1234)
+    with torch.device(dev):
+        model = LlamaForCausalLM(cfg).to(torch.bfloat16)
+    model.train()
+    model.config.use_cache = False
+    net = model
+    if dist is not None:
+        net = nn.parallel.DistributedDataParallel(model, device_ids=[dev.index], gradient_as_bucket_view=True)
+    params = [p for p in model.parameters() if p.requires_grad]
+    master = [p.detach().float().clone() for p in params]          # float32 master weights
+    opt = torch.optim.AdamW(master, lr=1e-4, weight_decay=0.01, fused=True)
+    g = torch.Generator(dev).manual_seed(7 + (dist.get_rank() if dist is not None else 0))
+    ids = torch.randint(0, cfg.vocab_size, (micro_batch, seq), device=dev, generator=g)
+
+    def step():
+        out = net(input_ids=ids, labels=ids)
+        out.loss.backward()
+        for m_, p_ in zip(master, params):
+            m_.grad = p_.grad.float()
+            p_.grad = None
+        opt.step()
+        torch._foreach_copy_(params, master)                         # bf16 <- float32 master
+        opt.zero_grad(set_to_none=True)
+        return out.loss.detach()
+
+    for _ in range(warmup):
+        loss = step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    l0 = _C.launch_count()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        loss = step()
+    t1.record()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    ms = t0.elapsed_time(t1) / steps
+    if dist is not None:
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t[0])
+    n_params = sum(p.numel() for p in params)
+    res = {"tokens_per_s": world * micro_batch * seq / (ms * 1e-3), "ms_per_step": ms, "loss": float(loss),
+           "params": n_params, "patched": patched, "tokens_per_gpu": micro_batch * seq, "steps": steps,
+           "fused_kernel_launches_per_step": (_C.launch_count() - l0) / steps,
+           "peak_mem_GB": torch.cuda.max_memory_allocated(dev) / 1e9}
+    del opt, master, net, model
+    torch.cuda.empty_cache()
+    return res
+
+
 # -------------------------------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -351,6 +419,11 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-tokens", type=int, default=8192)
+    ap.add_argument("--workload", default="opset", choices=["opset", "llama1b", "llama1b-unpatched"],
+                    help="opset (default): the fused operator set; llama1b: only the Llama-1B training step with "
+                         "the patch; llama1b-unpatched: the same with stock HuggingFace modules")
+    ap.add_argument("--train-step", action="store_true",
+                    help="after the operator set, also time the patched Llama-1B training step (adds ~1 min)")
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the tokens per GPU (a multiple of the config's sequence length); smaller "
                          "cases are for profiler captures, not for reported numbers")
@@ -403,7 +476,21 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])
 
+    if args.workload != "opset":
+        res = run_llama1b(dev, dist, world, max(1, min(args.steps, 10)), 2, patched=args.workload == "llama1b")
+        if rank == 0:
+            print(json.dumps({"metric": "llama1b_train_tokens_per_s", "value": res["tokens_per_s"], "unit": "tokens/s",
+                              "n_gpus": world, "steps": res["steps"], "warmup": 2, "ms_per_step": res["ms_per_step"],
+                              "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                              "data": "synthetic", "config": {"workload": "random-init Llama-style 1B decoder, 16 layers, hidden "
+                              "2048, 32q/8kv heads, FFN 8192, vocab 128256, micro-batch 4 x 4096 per GPU, AdamW on float32 "
+                              "master weights, DDP", "patched": res["patched"]}, "detail": res}))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
     ops = OpSet(cfg, dev, cfg["seed"] + rank)
+    n_rows = ops.M
     ab = algorithmic_bytes(cfg, ops.M, ops.ignored_frac)
     step_bytes = sum(ab.values())
     sampler = ClockSampler(local_rank)
@@ -429,12 +516,21 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         gbs, dt, M, cores = run_cpu_baseline(cfg, args.cpu_tokens, 2, 1, cfg["seed"])
         cpu = {"value": gbs, "unit": unit, "cores": cores, "kind": "port",
-               "sample": f"{M} of {ops.M} tokens, all four ops fwd+bwd, float32 autograd on host, {dt:.2f} s per pass"}
+               "sample": f"{M} of {n_rows} tokens, all four ops fwd+bwd, float32 autograd on host, {dt:.2f} s per pass"}
+
+    train = None
+    if args.train_step:
+        del ops
+        torch.cuda.empty_cache()
+        try:
+            train = run_llama1b(dev, dist, world, 5, 2, patched=True)
+        except Exception as e:  # noqa: BLE001 - the operator-set line must survive a failure here
+            train = {"error": f"{type(e).__name__}: {e}"[:300]}
 
     if rank == 0:
         ce = per_op["cross_entropy"]
         # the capture is of the V = 128256 bf16 kernel; other vocabularies have no capture
-        traffic = CE_TRAFFIC_BYTES_PER_ROW * ops.M if (CE_TRAFFIC_BYTES_PER_ROW and cfg["vocab"] == 128256) else None
+        traffic = CE_TRAFFIC_BYTES_PER_ROW * n_rows if (CE_TRAFFIC_BYTES_PER_ROW and cfg["vocab"] == 128256) else None
         out = {"metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": warmup,
                "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
                "data": "synthetic", "config": config, "frac_of_peak": value / world / peak, "per_op": per_op,
@@ -445,6 +541,8 @@ def main():
             out["e2e"] = e2e
         if cpu is not None:
             out["cpu_baseline"] = cpu
+        if train is not None:
+            out["llama1b_train_step"] = train
         print(json.dumps(out))
     if dist is not None:
         dist.destroy_process_group()

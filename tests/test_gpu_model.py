@@ -1,0 +1,75 @@
+"""End to end: a small HuggingFace Llama / Qwen2 with `from mdy_triton.replace_kernel import *` must give
+the loss and gradients of the stock model (reference's own check: Easy-Tutorials/09-test-kernel-speed.ipynb
+cells 3-7 compare gradients before and after the patch).  The stock model runs in a child process because
+the patch is process-wide and irreversible."""
+import json
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+
+CHILD = r"""
+import json, sys, torch
+sys.path.insert(0, {root!r})
+family, patched, dtype = sys.argv[1], sys.argv[2] == "1", getattr(torch, sys.argv[3])
+if patched:
+    from mdy_triton.replace_kernel import *  # noqa
+import transformers
+cfg_cls, model_cls = {{"llama": (transformers.LlamaConfig, transformers.LlamaForCausalLM),
+                      "qwen2": (transformers.Qwen2Config, transformers.Qwen2ForCausalLM)}}[family]
+cfg = cfg_cls(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+              vocab_size=2048, max_position_embeddings=128, rms_norm_eps=1e-5, attn_implementation="sdpa",
+              tie_word_embeddings=False)
+torch.manual_seed(0)
+model = model_cls(cfg).to("cuda").to(dtype)
+g = torch.Generator().manual_seed(1)
+ids = torch.randint(0, 2048, (3, 64), generator=g).cuda()
+labels = ids.clone(); labels[0, :10] = -100
+out = model(input_ids=ids, labels=labels)
+out.loss.backward()
+res = {{"loss": float(out.loss), "logits_shape": list(out.logits.shape)}}
+for name in ("model.embed_tokens.weight", "model.layers.0.input_layernorm.weight", "model.layers.1.post_attention_layernorm.weight",
+             "model.layers.0.self_attn.q_proj.weight", "model.layers.1.mlp.gate_proj.weight", "model.norm.weight", "lm_head.weight"):
+    p = dict(model.named_parameters())[name]
+    res[name] = [float(p.grad.float().norm()), float(p.grad.float().flatten()[:64].sum())]
+with torch.no_grad():
+    res["eval_loss"] = float(model(input_ids=ids, labels=labels).loss)
+    gen = model.generate(ids[:1, :8], max_new_tokens=4, do_sample=False)
+    res["generated"] = gen[0].tolist()
+print("RESULT " + json.dumps(res))
+"""
+
+
+def _run(family, patched, dtype):
+    r = subprocess.run([sys.executable, "-c", CHILD.format(root=str(ROOT)), family, "1" if patched else "0", dtype],
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-3000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+    return json.loads(line[7:])
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen2"])
+def test_patched_model_matches_stock_model_fp32(family):
+    a = _run(family, False, "float32")
+    b = _run(family, True, "float32")
+    assert a["logits_shape"] == b["logits_shape"]
+    assert abs(a["loss"] - b["loss"]) <= 1e-4 * max(1.0, abs(a["loss"]))
+    assert abs(a["eval_loss"] - b["eval_loss"]) <= 1e-4 * max(1.0, abs(a["eval_loss"]))
+    assert a["generated"] == b["generated"]
+    for k, v in a.items():
+        if isinstance(v, list) and len(v) == 2 and k not in ("logits_shape",):
+            assert abs(v[0] - b[k][0]) <= 2e-3 * max(1e-6, abs(v[0])), (k, v, b[k])
+
+
+def test_patched_model_matches_stock_model_bf16():
+    a = _run("llama", False, "bfloat16")
+    b = _run("llama", True, "bfloat16")
+    assert abs(a["loss"] - b["loss"]) <= 2e-2 * max(1.0, abs(a["loss"]))
+    for k, v in a.items():
+        if isinstance(v, list) and len(v) == 2 and k != "logits_shape":
+            assert abs(v[0] - b[k][0]) <= 5e-2 * max(1e-6, abs(v[0])), (k, v, b[k])
