@@ -375,7 +375,8 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
             m_.grad = p_.grad.float()
             p_.grad = None
         opt.step()
-        torch._foreach_copy_(params, master)                         # bf16 <- float32 master
+        with torch.no_grad():
+            torch._foreach_copy_(params, master)                     # bf16 <- float32 master
         opt.zero_grad(set_to_none=True)
         return out.loss.detach()
 
