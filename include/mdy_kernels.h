@@ -61,13 +61,14 @@ const char* mdy_status_string(int status);
 #define MDY_TUNE_NORM_CTAS_PER_SM 2  /* persistent-grid width of the norm kernels, in CTAs per SM  */
 #define MDY_TUNE_SWIGLU_UNROLL 3     /* 16-byte vectors per thread in SwiGLU (1, 2 or 4)           */
 #define MDY_TUNE_CE_FUSED_IMPL 4     /* 0 auto, 1 row-per-CTA kernel, 2 cluster kernel staging the row in shared
-                                        memory, 3 cluster kernel keeping the row's exponentials in registers */
+                                        memory, 3 cluster kernel keeping the row's exponentials in registers,
+                                        4 cluster kernel caching the exponentials in shared memory */
 #define MDY_TUNE_ROPE_THREADS 5      /* threads per CTA of the RoPE kernel                         */
 #define MDY_TUNE_CE_CLUSTER_SLICE_KB 6 /* largest slice of a row one CTA of the cluster kernel stages (KiB) */
 #define MDY_TUNE_CE_CLUSTER_THREADS 7  /* threads per CTA of the cluster kernel: 512 or 1024          */
 #define MDY_TUNE_CE_CLUSTER_VPC 8      /* 16-byte vectors per thread per chunk there: 1, 2 or 4       */
-#define MDY_TUNE_CE_REG_SHAPE 9        /* register-resident cluster kernel: 0/3 = 512 threads x 8 vectors,
-                                          1 = 256x8, 2 = 512x4, 4 = 1024x4                              */
+#define MDY_TUNE_CE_REG_SHAPE 9        /* impl 3: 0/3 = 512 threads x 8 vectors, 1 = 256x8, 2 = 512x4, 4 = 1024x4;
+                                          impl 4 / auto: 0 = smallest CTA that fits, 1 = 512, 2 = 1024 threads */
 #define MDY_TUNE_COUNT 10
 int mdy_set_tunable(int id, int value);
 /* Kernels that wait on hardware barriers bound every wait; if one ever expires they record a non-zero

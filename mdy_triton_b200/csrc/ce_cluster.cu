@@ -127,6 +127,12 @@ struct ClusterArgs {
   int slice_bytes_aligned;
 };
 
+#ifdef MDY_CE_TIMING
+#define MDY_TICK(i) { const long long t_ = clock64(); tacc[i] += t_ - tlast; tlast = t_; }
+#else
+#define MDY_TICK(i)
+#endif
+
 // Branch-free merge of (m, s) with (om, os): one exp, no divergence.  Maxima are clamped to -1e37 so
 // two empty operands (-inf, 0) do not produce inf - inf.
 __device__ __forceinline__ void merge_nb(float& m, float& s, float om, float os) {
@@ -230,6 +236,10 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
   uint32_t nloaded = 0;
   bool dead = false;
   const uint32_t my_s = slice_s + (uint32_t)tid * 16u;
+#ifdef MDY_CE_TIMING
+  long long tacc[6] = {0, 0, 0, 0, 0, 0};
+  long long tlast = clock64();
+#endif
   for (; row < a.M; row += ncl) {
     const int64_t label = a.labels[row];
     const bool cur_valid = label != MDY_IGNORE_INDEX;
@@ -248,6 +258,7 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
       continue;
     }
 
+    MDY_TICK(0)
     // ---- sweep 1: (max, sum-exp) of the slice as its chunks land ----
     const uint32_t parity = nloaded & 1u;
     float m = -INFINITY, s0 = 0.f, s1 = 0.f;
@@ -268,6 +279,7 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
       }
       stats_chunk<T, VPC>(q, m, s0, s1);
     }
+    MDY_TICK(1)
     float s = s0 + s1;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -277,6 +289,7 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
     }
     if (lane == 0) { red[warp] = m; red[32 + warp] = s; }
     __syncthreads();
+    MDY_TICK(2)
     int loc = -1;  // label position inside this CTA's slice, in elements
     if (label >= 0 && label < a.V) {
       const int64_t l = label - slice_elem0;
@@ -304,6 +317,7 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
     // two exchange slots suffice: a peer cannot send for row n+2 before it has this CTA's message for
     // row n+1, which leaves only after the reads of row n below
     mbar_wait(full_s + 8 * (kMaxChunks + (nloaded & 1u)), (nloaded >> 1) & 1u, dead);
+    MDY_TICK(3)
     float gm = -INFINITY, gs = 0.f, xl = 0.f;
     {
       const float* x = xchg + (int)(nloaded & 1u) * kMaxCluster * 4;
@@ -351,7 +365,15 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
       const float p = fast_exp2(fmaf(xl, kLog2e, -lse * kLog2e));
       dlogits[row * a.rs + slice_elem0 + loc] = from_float<T>((p - 1.f) * g);
     }
+    MDY_TICK(4)
   }
+#ifdef MDY_CE_TIMING
+  if (blockIdx.x < 8 && (tid == 0 || tid == 40 || tid == NT - 1)) {
+    float* o = a.lse + a.M + (blockIdx.x * 3 + (tid == 0 ? 0 : tid == 40 ? 1 : 2)) * 8;
+    for (int i = 0; i < 5; ++i) o[i] = (float)tacc[i];
+    o[5] = (float)nloaded;
+  }
+#endif
 }
 
 template <typename T, int NT, int VPC>
@@ -530,10 +552,7 @@ __global__ void __launch_bounds__(NT, (NT * NVEC <= 2048 ? 2 : 1)) ce_regrow_ker
   bool dead = false;
 #ifdef MDY_CE_TIMING
   long long tacc[6] = {0, 0, 0, 0, 0, 0};
-#define MDY_TICK(i) { const long long t_ = clock64(); tacc[i] += t_ - tlast; tlast = t_; }
   long long tlast = clock64();
-#else
-#define MDY_TICK(i)
 #endif
   for (int64_t row = cid; row < a.M; row += ncl) {
     const int64_t label = a.labels[row];
@@ -739,6 +758,296 @@ int launch_regrow(const ClusterArgs& a, cudaStream_t st) {
   }
 }
 
+
+// =================================================================================================
+// Exp-cache variant (the default where the row fits): one exp per logit with 16-32 warps per SM.
+//
+// Sweep 1 computes e = exp2(x*log2e - ref*log2e) (ref = the thread's running max when it processed
+// the chunk) and parks it as float32 in a per-CTA shared-memory buffer; sweep 2 reads it back,
+// multiplies by one factor per (thread, chunk), exp2((ref - lse)*log2e) * g, packs and stores.  The
+// bf16 logits only pass through a ring of NVEC bulk-copy buffers (one row deep): a buffer is released
+// the moment its 16 bytes per thread are in registers and is refilled with the same chunk of the
+// cluster's next row, so the next row streams in while the current one is still being processed.
+// A thread reads in sweep 2 exactly the shared-memory words it wrote in sweep 1, so the float32
+// buffer needs no barrier at all.  The buffer is split into 16-byte planes so that both the stores
+// and the loads of a warp are conflict-free.
+//   NT = 512 : up to 2048 vectors per CTA, 96 KB of shared memory -> two CTAs per SM (a CTA's
+//              reduction and exchange overlap the other's sweeps); rows up to 8 * 2048 vectors.
+//   NT = 1024: up to 4096 vectors per CTA, 192 KB -> one CTA per SM; rows up to 8 * 4096 vectors.
+// =================================================================================================
+template <typename T, int NT>
+__global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) ce_expcache_kernel(ClusterArgs a) {
+  constexpr int VE = VecInfo<T>::kElems;
+  constexpr int NW = NT / 32;
+  constexpr int NVEC = 4;
+  constexpr int EPV = VE / 4;                       // 16-byte planes of float32 per vector
+  constexpr uint32_t SLOT_BYTES = NT * 16;
+  constexpr uint32_t PLANE_BYTES = NVEC * NT * 16;
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_raw + (size_t)NVEC * SLOT_BYTES + (size_t)EPV * PLANE_BYTES);
+  float* xchg = reinterpret_cast<float*>(bars + 2 * NVEC + 2);   // full[NVEC], empty[NVEC], xbar[2] | [2][kMaxCluster][4]
+  float* red = xchg + 2 * kMaxCluster * 4;                       // [72]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t crank = cluster_ctarank();
+  const int C = a.C;
+  const int cid = blockIdx.x / C, ncl = gridDim.x / C;
+  const int64_t nvec_total = a.V / VE;
+  const int64_t v0 = (int64_t)crank * a.vpc;
+  int my_nvec = (int)(nvec_total - v0 < a.vpc ? nvec_total - v0 : a.vpc);
+  if (my_nvec < 0) my_nvec = 0;
+  const int nj = (my_nvec + NT - 1) / NT;   // chunks of this CTA's slice, <= NVEC
+  const uint32_t ring_s = smem_u32(smem_raw);
+  const uint32_t ebuf_s = ring_s + NVEC * SLOT_BYTES + (uint32_t)tid * 16u;   // this thread's column of the planes
+  const uint32_t full_s = smem_u32(bars);
+  const uint32_t empty_s = full_s + 8 * NVEC;
+  const uint32_t xbar_s = empty_s + 8 * NVEC;
+  const T* logits = reinterpret_cast<const T*>(a.logits);
+  T* dlogits = reinterpret_cast<T*>(a.dlogits);
+  const int slice_elem0 = (int)(v0 * VE);
+
+  if (tid == 0) {
+    for (int k = 0; k < NVEC; ++k) {
+      mbar_init(full_s + 8 * k, 1);
+      mbar_init(empty_s + 8 * k, NW);
+    }
+    mbar_init(xbar_s, 1);
+    mbar_init(xbar_s + 8, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  cluster_sync_all();  // all CTAs of the cluster run before anyone writes a peer's shared memory
+  const float g = a.ghost * (a.gdev ? *a.gdev : 1.f);
+
+  // ---- producer state, used by thread 0 only ----
+  int64_t prow = cid;
+  auto next_labelled_row = [&]() -> int64_t {
+    while (prow < a.M && a.labels[prow] == MDY_IGNORE_INDEX) prow += ncl;
+    const int64_t r = prow;
+    if (prow < a.M) prow += ncl;
+    return r;  // >= M: none left
+  };
+  auto issue = [&](int64_t row, int j) {
+    const int first = j * NT;
+    int nv = my_nvec - first;
+    if (nv <= 0) return;
+    if (nv > NT) nv = NT;
+    const char* src = reinterpret_cast<const char*>(logits + row * a.rs) + (v0 + first) * 16;
+    mbar_expect_tx(full_s + 8 * j, (uint32_t)nv * 16u);
+    bulk_g2s(ring_s + (uint32_t)j * SLOT_BYTES, src, (uint32_t)nv * 16u, full_s + 8 * j);
+  };
+  int64_t r_next = a.M;  // thread 0: the labelled row after the one currently in the ring
+  if (tid == 0) {
+    const int64_t r = next_labelled_row();
+    if (r < a.M)
+      for (int j = 0; j < nj; ++j) issue(r, j);
+    r_next = next_labelled_row();
+  }
+
+  uint32_t n_cons = 0;  // labelled rows consumed so far
+  bool dead = false;
+  int64_t label = cid < a.M ? a.labels[cid] : MDY_IGNORE_INDEX;
+  for (int64_t row = cid; row < a.M; row += ncl) {
+    // the next row's label is fetched a whole row ahead of its use
+    const int64_t label_next = row + ncl < a.M ? a.labels[row + ncl] : MDY_IGNORE_INDEX;
+    T* dst = dlogits + row * a.rs + (int64_t)slice_elem0 + (int64_t)tid * VE;
+    if (label == MDY_IGNORE_INDEX) {
+      if (crank == 0 && tid == 0) { a.losses[row] = 0.f; a.lse[row] = 0.f; }
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      for (int v = tid; v < my_nvec; v += NT) st_stream(dst + (int64_t)(v - tid) * VE, z);
+      label = label_next;
+      continue;
+    }
+    const uint32_t par = n_cons & 1u;
+    int loc = -1;
+    if (label >= 0 && label < a.V) {
+      const int64_t l = label - slice_elem0;
+      if (l >= 0 && l < (int64_t)my_nvec * VE) loc = (int)l;
+    }
+    const int loc_vec = loc >= 0 ? loc / VE : -1;
+
+    // ---- sweep 1 ----
+    float ref[NVEC];
+    float m = -INFINITY, s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NVEC; ++j) {
+      if (j < nj) {
+        mbar_wait(full_s + 8 * j, par, dead);
+        const int v = j * NT + tid;
+        const uint4 q = v < my_nvec ? lds128(ring_s + (uint32_t)j * SLOT_BYTES + (uint32_t)tid * 16u) : neg_inf_vec<T>();
+        float f[VE];
+        unpack<T>(q, f);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty_s + 8 * j);       // this warp's part of the buffer is in registers
+        if (tid == 0 && r_next < a.M && j >= 1) {          // refill the buffer released one step ago
+          mbar_wait(empty_s + 8 * (j - 1), par, dead);
+          issue(r_next, j - 1);
+        }
+        const float vm = vec_max<T>(q);
+        if (vm > m) {
+          const float r = fast_exp2((fmaxf(m, -1e37f) - vm) * kLog2e);
+          s0 *= r; s1 *= r;
+          m = vm;
+        }
+        ref[j] = m;
+        const float nm2 = -fmaxf(m, -1e37f) * kLog2e;
+        if (v == loc_vec) {  // the label's logit, for the loss
+          float xl = 0.f;
+#pragma unroll
+          for (int k = 0; k < VE; ++k)
+            if (k == loc - loc_vec * VE) xl = f[k];
+          red[70] = xl;
+        }
+#pragma unroll
+        for (int k = 0; k < VE; ++k) f[k] = fast_exp2(fmaf(f[k], kLog2e, nm2));
+#pragma unroll
+        for (int k = 0; k < VE; k += 2) { s0 += f[k]; s1 += f[k + 1]; }
+#pragma unroll
+        for (int pl = 0; pl < EPV; ++pl) {
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(ebuf_s + (uint32_t)pl * PLANE_BYTES + (uint32_t)j * SLOT_BYTES),
+                       "f"(f[4 * pl]), "f"(f[4 * pl + 1]), "f"(f[4 * pl + 2]), "f"(f[4 * pl + 3])
+                       : "memory");
+        }
+      }
+    }
+    if (tid == 0) {
+      if (r_next < a.M) {
+        mbar_wait(empty_s + 8 * (nj - 1), par, dead);
+        issue(r_next, nj - 1);
+      }
+      r_next = next_labelled_row();
+    }
+    float s = s0 + s1;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const float os = __shfl_xor_sync(0xffffffffu, s, o);
+      merge_nb(m, s, om, os);
+    }
+    if (lane == 0) { red[warp] = m; red[32 + warp] = s; }
+    __syncthreads();
+    if (warp == 0) {
+      float wm = lane < NW ? red[lane] : -INFINITY;
+      float ws = lane < NW ? red[32 + lane] : 0.f;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float om = __shfl_xor_sync(0xffffffffu, wm, o);
+        const float os = __shfl_xor_sync(0xffffffffu, ws, o);
+        merge_nb(wm, ws, om, os);
+      }
+      if (lane == 0) {
+        // this CTA's (max, sum, label logit) to every CTA of the cluster, itself included
+        const float xl = loc >= 0 ? red[70] : 0.f;
+        const uint32_t xb = xbar_s + 8 * (n_cons & 1u);
+        const uint32_t slotx = smem_u32(xchg + ((int)(n_cons & 1u) * kMaxCluster + (int)crank) * 4);
+        mbar_expect_tx(xb, (uint32_t)C * 16u);
+        for (int p = 0; p < C; ++p) st_async_v4(slotx, xb, (uint32_t)p, wm, ws, xl, 0.f);
+      }
+    }
+    // two exchange slots suffice: a peer cannot send for row n+2 before it has this CTA's message for
+    // row n+1, which leaves only after the reads of row n below
+    mbar_wait(xbar_s + 8 * (n_cons & 1u), (n_cons >> 1) & 1u, dead);
+    float gm = -INFINITY, gs = 0.f, xl = 0.f;
+    {
+      const float* x = xchg + (int)(n_cons & 1u) * kMaxCluster * 4;
+      for (int p = 0; p < C; ++p) {
+        merge_nb(gm, gs, x[p * 4], x[p * 4 + 1]);
+        xl += x[p * 4 + 2];
+      }
+    }
+    const float lse = gm + logf(gs);
+    if (crank == 0 && tid == 0) {
+      a.losses[row] = (label >= 0 && label < a.V) ? lse - xl : 0.f;
+      a.lse[row] = lse;
+    }
+
+    // ---- sweep 2: from the float32 buffer this thread filled ----
+#pragma unroll
+    for (int j = 0; j < NVEC; ++j) {
+      if (j < nj) {
+        const int v = j * NT + tid;
+        if (v < my_nvec) {
+          const float fac = fast_exp2((ref[j] - lse) * kLog2e) * g;
+          float o[VE];
+#pragma unroll
+          for (int pl = 0; pl < EPV; ++pl) {
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(o[4 * pl]), "=f"(o[4 * pl + 1]), "=f"(o[4 * pl + 2]), "=f"(o[4 * pl + 3])
+                         : "r"(ebuf_s + (uint32_t)pl * PLANE_BYTES + (uint32_t)j * SLOT_BYTES)
+                         : "memory");
+          }
+#pragma unroll
+          for (int k = 0; k < VE; ++k) o[k] *= fac;
+          st_stream(dst + (int64_t)(j * NT) * VE, pack<T>(o));
+        }
+      }
+    }
+    if (loc >= 0 && (loc_vec % NT) == tid) {
+      const float p = fast_exp2((xl - lse) * kLog2e);
+      dlogits[row * a.rs + slice_elem0 + loc] = from_float<T>((p - 1.f) * g);
+    }
+    ++n_cons;
+    label = label_next;
+  }
+}
+
+template <typename T, int NT>
+int launch_expcache_nt(ClusterArgs a, cudaStream_t st) {
+  constexpr int VE = VecInfo<T>::kElems;
+  constexpr int NVEC = 4, EPV = VE / 4;
+  const int64_t nvec = a.V / VE;
+  const int C = (int)ceil_div(nvec, (int64_t)NT * NVEC);
+  if (C > kMaxCluster) return MDY_ERR_UNSUPPORTED;
+  const int64_t vpc = ceil_div(nvec, C);
+  if ((int64_t)(C - 1) * vpc >= nvec) return MDY_ERR_UNSUPPORTED;
+  a.C = C;
+  a.vpc = (int)vpc;
+  a.slice_bytes_aligned = 0;
+  const size_t smem = (size_t)NVEC * NT * 16 * (1 + EPV) + (size_t)(2 * NVEC + 2) * 8 + 2 * kMaxCluster * 4 * 4 + 72 * 4;
+  auto kern = ce_expcache_kernel<T, NT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = C; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(NT, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(C, 1, 1);
+  static thread_local int c_dev = -1, c_C = 0, c_max = 0;
+  int dev = 0;
+  (void)cudaGetDevice(&dev);
+  int max_clusters = 0;
+  if (dev == c_dev && C == c_C) {
+    max_clusters = c_max;
+  } else {
+    e = cudaOccupancyMaxActiveClusters(&max_clusters, kern, &cfg);
+    if (e != cudaSuccess || max_clusters < 1) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
+    c_dev = dev; c_C = C; c_max = max_clusters;
+  }
+  int64_t ncl = a.M < max_clusters ? a.M : max_clusters;
+  cfg.gridDim = dim3((unsigned)(ncl * C), 1, 1);
+  e = cudaLaunchKernelEx(&cfg, kern, a);
+  if (e != cudaSuccess) return (int)e;
+  return finish_launch(1);
+}
+
+// shape: 0 = smallest CTA that fits the row in <= 8 CTAs, 1 = 512 threads, 2 = 1024 threads
+template <typename T>
+int launch_expcache(const ClusterArgs& a, cudaStream_t st, int shape) {
+  constexpr int VE = VecInfo<T>::kElems;
+  if (a.V % VE != 0 || a.rs % VE != 0 || !aligned16(a.logits) || !aligned16(a.dlogits)) return MDY_ERR_UNSUPPORTED;
+  if (a.V >= ((int64_t)1 << 27)) return MDY_ERR_UNSUPPORTED;
+  if (shape != 2) {
+    const int rc = launch_expcache_nt<T, 512>(a, st);
+    if (rc != MDY_ERR_UNSUPPORTED || shape == 1) return rc;
+  }
+  return launch_expcache_nt<T, 1024>(a, st);
+}
+
 }  // namespace
 
 int ce_fused_cluster(const void* logits, void* dlogits, const int64_t* labels, float* losses, float* lse,
@@ -751,10 +1060,14 @@ int ce_fused_cluster(const void* logits, void* dlogits, const int64_t* labels, f
   const int impl = tunable(MDY_TUNE_CE_FUSED_IMPL);
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
-    // The shared-memory kernel is the default: with 32 warps per SM it keeps the issue slots 60 % busy.
-    // The register-resident kernel needs one exp per logit instead of two but leaves room for only
-    // 16 warps per SM and measured slower; it stays selectable for experiments.
+    // Default order: exp-cache kernel (one exp per logit), then the kernel that stages the whole slice
+    // in shared memory and recomputes the exp (rows too long for the former), else "unsupported" and the
+    // caller falls back to the row-per-CTA kernel.
     if (impl == 3) return launch_regrow<T>(a, st);
+    if (impl != 2) {
+      const int rc = launch_expcache<T>(a, st, tunable(MDY_TUNE_CE_REG_SHAPE));
+      if (rc != MDY_ERR_UNSUPPORTED || impl == 4) return rc;
+    }
     return launch_cluster<T>(a, st);
   });
 }

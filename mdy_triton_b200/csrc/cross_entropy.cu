@@ -345,7 +345,18 @@ int mdy_ce_fused(const void* logits, void* dlogits, const int64_t* labels, float
   }
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
-    ce_fused_kernel<T><<<(unsigned)M, ce_threads(), 0, (cudaStream_t)stream>>>(
+    // Optional residency cap: asking for 1/k of the SM's shared memory keeps at most k CTAs (rows) per
+    // SM in flight, which bounds the L2 footprint of the rows between their two sweeps.
+    size_t pad = 0;
+    const int per_sm = tunable(MDY_TUNE_CE_FUSED_CTAS_PER_SM);
+    if (per_sm > 0) {
+      pad = (size_t)(227 * 1024) / per_sm - 2048;
+      if (cudaFuncSetAttribute(ce_fused_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)pad) != cudaSuccess) {
+        (void)cudaGetLastError();
+        pad = 0;
+      }
+    }
+    ce_fused_kernel<T><<<(unsigned)M, ce_threads(), pad, (cudaStream_t)stream>>>(
         (const T*)logits, (T*)dlogits, labels, losses, lse, grad_scale_dev, grad_scale_host, V,
         row_stride, rows_vec_ok<T>(logits, dlogits, row_stride));
     return finish_launch(1);

@@ -114,9 +114,10 @@ def shifted_labels(labels):
     return F.pad(labels[..., 1:], (0, 1), value=-100)
 
 
-def make_causal_forward(original_forward):
+def make_causal_forward(original_forward, output_cls=CausalLMOutputWithPast, extra_fields=()):
     """Build ``<Model>ForCausalLM.forward``: the stock forward with the loss replaced by the fused
-    cross-entropy (reference llama.py:92-184)."""
+    cross-entropy (reference llama.py:92-184).  ``output_cls`` / ``extra_fields`` let a model family
+    return its own output type (Qwen2-VL adds ``rope_deltas``)."""
     params = inspect.signature(original_forward).parameters
     keep_name = "logits_to_keep" if "logits_to_keep" in params else "num_logits_to_keep"
 
@@ -141,27 +142,29 @@ def make_causal_forward(original_forward):
         if isinstance(outputs, tuple):  # legacy return_dict=False path
             output = (logits,) + outputs[1:]
             return (loss,) + output if loss is not None else output
-        return CausalLMOutputWithPast(loss=loss, logits=logits,
-                                      past_key_values=getattr(outputs, "past_key_values", None),
-                                      hidden_states=getattr(outputs, "hidden_states", None),
-                                      attentions=getattr(outputs, "attentions", None))
+        extra = {f: getattr(outputs, f, None) for f in extra_fields}
+        return output_cls(loss=loss, logits=logits,
+                          past_key_values=getattr(outputs, "past_key_values", None),
+                          hidden_states=getattr(outputs, "hidden_states", None),
+                          attentions=getattr(outputs, "attentions", None), **extra)
 
     causal_forward.__doc__ = make_causal_forward.__doc__
     return can_return_tuple(causal_forward)
 
 
 def patch_family(module, prefix, *, mlp=mlp_forward, rope=True, fuse_add_norm=True,
-                 decoder_cls=None, causal_cls=None):
+                 decoder_cls=None, causal_cls=None, norm_cls=None, mlp_cls=None, output_cls=CausalLMOutputWithPast,
+                 extra_fields=()):
     """Assign the five patched attributes on a ``transformers.models.<m>.modeling_<m>`` module
     (reference llama.py:186-190).  Idempotent."""
     if getattr(module, "_mdy_patched", False):
         return
     if rope:
         module.apply_rotary_pos_emb = fused_apply_rope
-    getattr(module, prefix + "RMSNorm").forward = rmsnorm_forward
-    getattr(module, prefix + "MLP").forward = mlp
+    getattr(module, norm_cls or prefix + "RMSNorm").forward = rmsnorm_forward
+    getattr(module, mlp_cls or prefix + "MLP").forward = mlp
     dec = getattr(module, decoder_cls or prefix + "DecoderLayer")
     dec.forward = make_decoder_layer_forward(dec.forward, fuse_add_norm)
     lm = getattr(module, causal_cls or prefix + "ForCausalLM")
-    lm.forward = make_causal_forward(lm.forward)
+    lm.forward = make_causal_forward(lm.forward, output_cls, extra_fields)
     module._mdy_patched = True

@@ -310,13 +310,13 @@ def test_swiglu_linearity_full_size():
 
 
 # ---------------------------------------------------------------------------------------- cross-entropy
-@pytest.fixture(params=["reg512x8", "reg256x8", "reg512x4", "reg1024x4", "smem", "row"], autouse=False)
+@pytest.fixture(params=["auto", "expcache512", "expcache1024", "reg512x8", "reg512x4", "smem", "row"], autouse=False)
 def fused_impl(request):
-    """Run a test under every one-pass implementation: the cluster kernel that keeps the row's
-    exponentials in registers (default where the shape fits; four thread/vector shapes), the cluster
-    kernel that stages the row in shared memory, and the row-per-CTA kernel both fall back to."""
-    impl = {"row": 1, "smem": 2}.get(request.param, 3)
-    shape = {"reg512x8": 0, "reg256x8": 1, "reg512x4": 2, "reg1024x4": 4}.get(request.param, 0)
+    """Run a test under every one-pass implementation: the default dispatch, the cluster kernel that
+    caches the exponentials in shared memory (two CTA sizes), the one that keeps them in registers, the
+    one that stages the whole slice and recomputes, and the row-per-CTA kernel all of them fall back to."""
+    impl = {"auto": 0, "row": 1, "smem": 2, "expcache512": 4, "expcache1024": 4}.get(request.param, 3)
+    shape = {"reg512x8": 0, "reg512x4": 2, "expcache512": 1, "expcache1024": 2}.get(request.param, 0)
     _C.set_tunable(_C.TUNE_CE_FUSED_IMPL, impl)
     _C.set_tunable(_C.TUNE_CE_REG_SHAPE, shape)
     yield request.param

@@ -35,6 +35,16 @@ def test_mistral_and_phi3_are_patched():
     assert m.Phi3MLP.forward is _common.mlp_forward_fused_proj
 
 
+def test_qwen2_vl_text_stack_is_patched():
+    import transformers.models.qwen2_vl.modeling_qwen2_vl as m
+    assert m.Qwen2VLRMSNorm.forward is _common.rmsnorm_forward
+    assert m.Qwen2MLP.forward is _common.mlp_forward
+    assert m.Qwen2VLDecoderLayer.forward.__module__ == _common.__name__
+    assert "pixel_values" not in inspect.signature(m.Qwen2VLDecoderLayer.forward).parameters
+    assert "labels" in inspect.signature(m.Qwen2VLForConditionalGeneration.forward).parameters
+    assert m.apply_multimodal_rotary_pos_emb.__module__ == m.__name__   # left alone, as in the reference
+
+
 def test_reference_import_paths_resolve():
     from mdy_triton.replace_kernel import trigger
     from mdy_triton.replace_kernel.llama import module, trigger as t2
