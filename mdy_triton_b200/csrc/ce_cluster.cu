@@ -240,11 +240,15 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
   long long tacc[6] = {0, 0, 0, 0, 0, 0};
   long long tlast = clock64();
 #endif
-  for (; row < a.M; row += ncl) {
-    const int64_t label = a.labels[row];
+  // labels are fetched one row ahead, so the global load is never on the row's critical path
+  int64_t label_after = MDY_IGNORE_INDEX;
+  int64_t label = row < a.M ? a.labels[row] : MDY_IGNORE_INDEX;
+  int64_t label_next = row + ncl < a.M ? a.labels[row + ncl] : MDY_IGNORE_INDEX;
+  for (; row < a.M; row += ncl, label = label_next, label_next = label_after) {
     const bool cur_valid = label != MDY_IGNORE_INDEX;
     const int64_t nrow = row + ncl;
-    const bool next_valid = nrow < a.M && a.labels[nrow] != MDY_IGNORE_INDEX;
+    const bool next_valid = nrow < a.M && label_next != MDY_IGNORE_INDEX;
+    label_after = nrow + ncl < a.M ? a.labels[nrow + ncl] : MDY_IGNORE_INDEX;
     T* dst = dlogits + row * a.rs + (int64_t)slice_elem0 + (int64_t)tid * VE;
 
     if (!cur_valid) {
@@ -847,6 +851,10 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) ce_expcache_kernel(Cl
   uint32_t n_cons = 0;  // labelled rows consumed so far
   bool dead = false;
   int64_t label = cid < a.M ? a.labels[cid] : MDY_IGNORE_INDEX;
+#ifdef MDY_CE_TIMING
+  long long tacc[6] = {0, 0, 0, 0, 0, 0};
+  long long tlast = clock64();
+#endif
   for (int64_t row = cid; row < a.M; row += ncl) {
     // the next row's label is fetched a whole row ahead of its use
     const int64_t label_next = row + ncl < a.M ? a.labels[row + ncl] : MDY_IGNORE_INDEX;
@@ -858,6 +866,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) ce_expcache_kernel(Cl
       label = label_next;
       continue;
     }
+    MDY_TICK(0)
     const uint32_t par = n_cons & 1u;
     int loc = -1;
     if (label >= 0 && label < a.V) {
@@ -910,6 +919,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) ce_expcache_kernel(Cl
         }
       }
     }
+    MDY_TICK(1)
     if (tid == 0) {
       if (r_next < a.M) {
         mbar_wait(empty_s + 8 * (nj - 1), par, dead);
@@ -926,6 +936,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) ce_expcache_kernel(Cl
     }
     if (lane == 0) { red[warp] = m; red[32 + warp] = s; }
     __syncthreads();
+    MDY_TICK(2)
     if (warp == 0) {
       float wm = lane < NW ? red[lane] : -INFINITY;
       float ws = lane < NW ? red[32 + lane] : 0.f;
@@ -947,6 +958,7 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) ce_expcache_kernel(Cl
     // two exchange slots suffice: a peer cannot send for row n+2 before it has this CTA's message for
     // row n+1, which leaves only after the reads of row n below
     mbar_wait(xbar_s + 8 * (n_cons & 1u), (n_cons >> 1) & 1u, dead);
+    MDY_TICK(3)
     float gm = -INFINITY, gs = 0.f, xl = 0.f;
     {
       const float* x = xchg + (int)(n_cons & 1u) * kMaxCluster * 4;
@@ -988,7 +1000,15 @@ __global__ void __launch_bounds__(NT, (NT <= 512 ? 2 : 1)) ce_expcache_kernel(Cl
     }
     ++n_cons;
     label = label_next;
+    MDY_TICK(4)
   }
+#ifdef MDY_CE_TIMING
+  if (blockIdx.x < 8 && (tid == 0 || tid == 40 || tid == NT - 1)) {
+    float* o = a.lse + a.M + (blockIdx.x * 3 + (tid == 0 ? 0 : tid == 40 ? 1 : 2)) * 8;
+    for (int i = 0; i < 5; ++i) o[i] = (float)tacc[i];
+    o[5] = (float)n_cons;
+  }
+#endif
 }
 
 template <typename T, int NT>
@@ -1060,14 +1080,13 @@ int ce_fused_cluster(const void* logits, void* dlogits, const int64_t* labels, f
   const int impl = tunable(MDY_TUNE_CE_FUSED_IMPL);
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
-    // Default order: exp-cache kernel (one exp per logit), then the kernel that stages the whole slice
-    // in shared memory and recomputes the exp (rows too long for the former), else "unsupported" and the
-    // caller falls back to the row-per-CTA kernel.
+    // Default: the kernel that stages the whole slice in shared memory and recomputes the exp — big
+    // CTAs (one per SM, 64 K logits per CTA and row) amortise the per-row reduction and exchange best.
+    // The one-exp variants (3: exponentials in registers, 4: cached in shared memory) split a row over
+    // more, smaller CTAs; on-device timing showed their per-row exchange latency dominating, so they
+    // are kept selectable for experiments only.
     if (impl == 3) return launch_regrow<T>(a, st);
-    if (impl != 2) {
-      const int rc = launch_expcache<T>(a, st, tunable(MDY_TUNE_CE_REG_SHAPE));
-      if (rc != MDY_ERR_UNSUPPORTED || impl == 4) return rc;
-    }
+    if (impl == 4) return launch_expcache<T>(a, st, tunable(MDY_TUNE_CE_REG_SHAPE));
     return launch_cluster<T>(a, st);
   });
 }
