@@ -409,6 +409,63 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
     return res
 
 
+# ------------------------------------------------------------------------------ vocab-parallel CE sweep
+def run_vpce(dev, dist, world, rank, steps, warmup):
+    """BASELINE config 5: 16384 tokens, vocab in {32000, 128256, 151936, 256000} sharded over the ranks,
+    logits N(0, sigma^2) with sigma in {1, 4}, 5 % of the labels -100, bf16, gradient written in place.
+    Per step and rank: local sweep (mdy_ce_fwd, split mode) -> one all_gather of [2, M] float32 ->
+    mdy_ce_vp_combine -> local gradient sweep (mdy_ce_bwd).  The collective is inside the timed region."""
+    from mdy_triton_b200.core import vocab_parallel as vp
+    M = 16384
+    cases = []
+    for V in (32000, 128256, 151936, 256000):
+        for sigma in (1.0, 4.0):
+            vs = V // world
+            g = torch.Generator(dev).manual_seed(3 + rank)
+            shard = torch.randn(M, vs, device=dev, dtype=torch.bfloat16, generator=g).mul_(sigma)
+            gl = torch.Generator(dev).manual_seed(3)                       # labels identical on every rank
+            labels = torch.randint(0, vs * world, (M,), device=dev, generator=gl)
+            labels[torch.rand(M, device=dev, generator=gl) < 0.05] = -100
+            f_ign = float((labels == -100).float().mean())
+            dl = torch.full((M,), 1.0 / M, device=dev)
+            stats = torch.empty(2, M, dtype=torch.float32, device=dev)
+            gathered = torch.empty(world, 2, M, dtype=torch.float32, device=dev)
+            work = torch.empty_like(shard)
+
+            def timed():
+                vp._local_forward(work, labels, vs * rank, stats)
+                if dist is not None:
+                    dist.all_gather_into_tensor(gathered.view(-1), stats.view(-1))
+                else:
+                    gathered[0].copy_(stats)
+                losses, lse = vp._combine(gathered, labels)
+                vp._local_backward(dl, work, labels, lse, work, vs * rank)
+                return losses
+            ms = []
+            for i in range(warmup + steps):
+                work.copy_(shard)                                         # restore the logits outside the timed region
+                torch.cuda.synchronize()
+                if dist is not None:
+                    dist.barrier()
+                e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+                e0.record(); losses = timed(); e1.record()
+                torch.cuda.synchronize()
+                if i >= warmup:
+                    ms.append(e0.elapsed_time(e1))
+            t = statistics.median(ms)
+            if dist is not None:
+                tt = torch.tensor([t], dtype=torch.float64, device=dev)
+                dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+                t = float(tt[0])
+            alg = M * vs * 2 * (2 - f_ign) * world
+            moved = M * vs * 2 * (3 - 2 * f_ign) * world
+            cases.append({"vocab": vs * world, "sigma": sigma, "ms": t, "algorithmic_GBps": alg / t / 1e6,
+                          "moved_GBps": moved / t / 1e6, "loss": float(losses.sum() / (labels != -100).sum())})
+            del shard, work
+            torch.cuda.empty_cache()
+    return cases
+
+
 # -------------------------------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -420,7 +477,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-tokens", type=int, default=8192)
-    ap.add_argument("--workload", default="opset", choices=["opset", "llama1b", "llama1b-unpatched"],
+    ap.add_argument("--workload", default="opset", choices=["opset", "llama1b", "llama1b-unpatched", "vpce"],
                     help="opset (default): the fused operator set; llama1b: only the Llama-1B training step with "
                          "the patch; llama1b-unpatched: the same with stock HuggingFace modules")
     ap.add_argument("--train-step", action="store_true",
@@ -477,6 +534,19 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])
 
+    if args.workload == "vpce":
+        cases = run_vpce(dev, dist, world, rank, max(3, min(args.steps, 10)), 3)
+        if rank == 0:
+            peak, _ = measured_peak()
+            val = statistics.mean(c["algorithmic_GBps"] for c in cases)
+            print(json.dumps({"metric": "vocab_parallel_ce_fwd_bwd_algorithmic_hbm_throughput", "value": val, "unit": "GB/s",
+                              "n_gpus": world, "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
+                              "config": {"workload": "vocab-parallel cross-entropy sweep, 16384 tokens, vocab sharded over the GPUs, "
+                                         "one all-gather of per-row statistics inside the timed region, gradient in place"},
+                              "frac_of_peak_per_gpu": val / world / peak, "cases": cases}))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     if args.workload != "opset":
         res = run_llama1b(dev, dist, world, max(1, min(args.steps, 10)), 2, patched=args.workload == "llama1b")
         if rank == 0:

@@ -69,7 +69,10 @@ const char* mdy_status_string(int status);
 #define MDY_TUNE_CE_CLUSTER_VPC 8      /* 16-byte vectors per thread per chunk there: 1, 2 or 4       */
 #define MDY_TUNE_CE_REG_SHAPE 9        /* impl 3: 0/3 = 512 threads x 8 vectors, 1 = 256x8, 2 = 512x4, 4 = 1024x4;
                                           impl 4 / auto: 0 = smallest CTA that fits, 1 = 512, 2 = 1024 threads */
-#define MDY_TUNE_COUNT 10
+#define MDY_TUNE_ROPE_HEADS_PER_THREAD 10 /* heads a RoPE thread rotates per work item: 1, 2 or 4       */
+#define MDY_TUNE_ROPE_GRID_PER_SM 11      /* cap of the RoPE grid, in CTAs per SM (grid-stride loop)       */
+#define MDY_TUNE_NORM_BWD_THREADS 12      /* smallest CTA of the norm backward kernels: 128, 256 or 512    */
+#define MDY_TUNE_COUNT 13
 int mdy_set_tunable(int id, int value);
 /* Kernels that wait on hardware barriers bound every wait; if one ever expires they record a non-zero
  * code in a device flag and run to completion with a wrong result instead of hanging.  This call

@@ -28,6 +28,9 @@ TUNE_CE_CLUSTER_SLICE_KB = 6
 TUNE_CE_CLUSTER_THREADS = 7
 TUNE_CE_CLUSTER_VPC = 8
 TUNE_CE_REG_SHAPE = 9
+TUNE_ROPE_HEADS_PER_THREAD = 10
+TUNE_ROPE_GRID_PER_SM = 11
+TUNE_NORM_BWD_THREADS = 12
 
 _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 

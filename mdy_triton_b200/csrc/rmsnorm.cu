@@ -196,22 +196,33 @@ norm_bwd_vec(const T* __restrict__ dy, const T* __restrict__ x, const void* __re
     }
   }
 
-  int it = 0;
-  for (int64_t base = (int64_t)blockIdx.x * gpc; base < M; base += (int64_t)gridDim.x * gpc, ++it) {
-    const int64_t row = base + gid;
+  // Software pipeline: the loads of the CTA's next row are issued before the current row's reduction
+  // (which contains a __syncthreads), so HBM requests stay in flight across the barrier.  Only where the
+  // register budget allows it (CTAs of up to 512 threads).
+  constexpr bool PF = MAXT <= 512;
+  uint4 xv[VPT], gv[VPT], dv[ADD ? VPT : 1];
+  uint4 nx[VPT], ng[VPT], nd[ADD ? VPT : 1];
+  float rstd = 0.f, nrstd = 0.f;
+  const int64_t step = (int64_t)gridDim.x * gpc;
+  auto fetch = [&](int64_t row, uint4* px, uint4* pg, uint4* pd, float& r) {
     const bool valid = row < M;
-    uint4 xv[VPT], gv[VPT];
-    uint4 dv[ADD ? VPT : 1];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = t + i * G;
       const bool on = valid && v < nvec;
-      xv[i] = on ? ld_stream(x + row * x_rs + (int64_t)v * VE) : make_uint4(0, 0, 0, 0);
-      gv[i] = on ? ld_stream(dy + row * dy_rs + (int64_t)v * VE) : make_uint4(0, 0, 0, 0);
-      if (ADD) dv[i] = (on && has_dres) ? ld_stream(dres + row * dres_rs + (int64_t)v * VE)
+      px[i] = on ? ld_stream(x + row * x_rs + (int64_t)v * VE) : make_uint4(0, 0, 0, 0);
+      pg[i] = on ? ld_stream(dy + row * dy_rs + (int64_t)v * VE) : make_uint4(0, 0, 0, 0);
+      if (ADD) pd[i] = (on && has_dres) ? ld_stream(dres + row * dres_rs + (int64_t)v * VE)
                                         : make_uint4(0, 0, 0, 0);
     }
-    const float rstd = valid ? rstd_in[row] : 0.f;
+    r = valid ? rstd_in[row] : 0.f;
+  };
+  fetch((int64_t)blockIdx.x * gpc + gid, xv, gv, dv, rstd);
+  int it = 0;
+  for (int64_t base = (int64_t)blockIdx.x * gpc; base < M; base += step, ++it) {
+    const int64_t row = base + gid;
+    const bool valid = row < M;
+    if (PF && base + step < M) fetch(row + step, nx, ng, nd, nrstd);
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
@@ -242,6 +253,16 @@ norm_bwd_vec(const T* __restrict__ dy, const T* __restrict__ x, const void* __re
         for (int e = 0; e < VE; ++e) o[e] += df[e];
       }
       if (valid && v < nvec) st_stream(dx + row * dx_rs + (int64_t)v * VE, pack<T>(o));
+    }
+    if (PF) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        xv[i] = nx[i]; gv[i] = ng[i];
+        if (ADD) dv[i] = nd[i];
+      }
+      rstd = nrstd;
+    } else if (base + step < M) {
+      fetch(row + step, xv, gv, dv, rstd);
     }
   }
 
@@ -348,7 +369,14 @@ inline int64_t vec_grid(int64_t M, const RowPlan& p, int per_sm_scale) {
 inline int bwd_per_sm(const RowPlan& p) {
   int t = tunable(MDY_TUNE_NORM_CTAS_PER_SM);
   if (t > 0) return t;
-  return p.BT >= 1024 ? 1 : 2;
+  // measured (hidden 4096, bf16): one 512-thread CTA per SM with the next row prefetched is fastest
+  return p.BT >= 512 ? 1 : 2;
+}
+
+// smallest CTA of the backward kernels (a row group of G threads may need more)
+inline int bwd_min_threads() {
+  const int t = tunable(MDY_TUNE_NORM_BWD_THREADS);
+  return (t == 128 || t == 256 || t == 512) ? t : 512;
 }
 
 inline int64_t scalar_grid(int64_t M) {
@@ -362,7 +390,7 @@ inline int64_t partial_rows(int64_t M, int64_t N) {
   constexpr int VE = VecInfo<T>::kElems;
   int64_t rows = scalar_grid(M);
   if (N % VE == 0) {
-    RowPlan p = plan_rows(N / VE, 512);
+    RowPlan p = plan_rows(N / VE, bwd_min_threads());
     if (p.vpt) {
       int64_t g = vec_grid(M, p, bwd_per_sm(p));
       if (g > rows) rows = g;
@@ -417,7 +445,7 @@ int launch_bwd(const void* dy_, const void* x_, const void* w, int w_dtype, cons
   bool vec = N % VE == 0 && aligned16(dy) && aligned16(x) && aligned16(dx) && dy_rs % VE == 0 &&
              x_rs % VE == 0 && dx_rs % VE == 0;
   if (ADD && dres) vec = vec && aligned16(dres) && dres_rs % VE == 0;
-  RowPlan p = vec ? plan_rows(N / VE, 512) : RowPlan{0, 0, 0, 0};
+  RowPlan p = vec ? plan_rows(N / VE, bwd_min_threads()) : RowPlan{0, 0, 0, 0};
   int64_t grid;
   if (M == 0) {
     grid = 0;  // nothing to sweep: the reduce below writes dw = 0

@@ -2,8 +2,9 @@
 //
 // Work item = (token, chunk of HPT heads, 16-byte column j of the first half of the head).  The
 // thread that owns column j of the first half also owns column j of the second half, so the rotation
-// is register-local.  The four cos/sin vectors of the token are loaded once per item and reused for
-// the HPT heads of the chunk; all 2*HPT activation loads are issued before the first use.  q heads
+// is register-local.  The four cos/sin vectors of the token are loaded once per item (they stay in
+// L1/L2 across the heads of a token) and reused for the HPT heads of the chunk; all 2*HPT activation
+// loads are issued before the first use.  HPT = 1 by default: fewest registers, most threads in flight.  q heads
 // and k heads of a token are addressed as one list of QH+KH heads, so one launch covers both tensors.
 // Input and output take independent (batch, head, position) strides: forward runs in place on the
 // [B, L, H, D] projection output, backward can read an arbitrarily strided gradient and write it in
@@ -143,10 +144,9 @@ rope_scalar(RopeArgs a) {
   }
 }
 
-template <typename T>
-int launch_rope(const RopeArgs& a, bool bwd, cudaStream_t st) {
+template <typename T, int HPT>
+int launch_rope_h(const RopeArgs& a, bool bwd, cudaStream_t st) {
   constexpr int VE = VecInfo<T>::kElems;
-  constexpr int HPT = 4;
   const int half = a.D / 2;
   auto ok = [&](int64_t s) { return s % VE == 0; };
   bool vec = half % VE == 0 && aligned16(a.cos) && aligned16(a.sin) &&
@@ -156,14 +156,16 @@ int launch_rope(const RopeArgs& a, bool bwd, cudaStream_t st) {
              ok(a.ki_sb) && ok(a.ki_sh) && ok(a.ki_sl) && ok(a.ko_sb) && ok(a.ko_sh) && ok(a.ko_sl) &&
              ok(a.cos_sb);
   int threads = tunable(MDY_TUNE_ROPE_THREADS);
-  if (threads < 32 || threads > 256 || (threads & 31)) threads = 256;
+  if (threads < 32 || threads > 256 || (threads & 31)) threads = 128;
   const int H = a.QH + a.KH;
   int64_t items;
   if (vec) items = (int64_t)a.B * a.L * (half / VE) * ((H + HPT - 1) / HPT);
   else items = (int64_t)a.B * a.L * H * half;
   if (items == 0) return MDY_OK;
   int64_t grid = ceil_div(items, threads);
-  const int64_t cap = (int64_t)(num_sms() > 0 ? num_sms() : 1) * 64;
+  int waves = tunable(MDY_TUNE_ROPE_GRID_PER_SM);
+  if (waves <= 0) waves = 64;
+  const int64_t cap = (int64_t)(num_sms() > 0 ? num_sms() : 1) * waves;
   if (grid > cap) grid = cap;
   if (vec) {
     if (bwd) rope_vec<T, true, HPT><<<(unsigned)grid, threads, 0, st>>>(a);
@@ -173,6 +175,17 @@ int launch_rope(const RopeArgs& a, bool bwd, cudaStream_t st) {
     else rope_scalar<T, false><<<(unsigned)grid, threads, 0, st>>>(a);
   }
   return finish_launch(1);
+}
+
+template <typename T>
+int launch_rope(const RopeArgs& a, bool bwd, cudaStream_t st) {
+  // default from an on-device sweep (32q/8kv heads x 128, bf16): one head per item and 128-thread CTAs
+  // (44 registers, full occupancy) beat 2 or 4 heads per item (75-115 registers) by 12 %
+  switch (tunable(MDY_TUNE_ROPE_HEADS_PER_THREAD)) {
+    case 2: return launch_rope_h<T, 2>(a, bwd, st);
+    case 4: return launch_rope_h<T, 4>(a, bwd, st);
+    default: return launch_rope_h<T, 1>(a, bwd, st);
+  }
 }
 
 }  // namespace

@@ -215,6 +215,24 @@ def test_rope_vs_oracle(b, l, qh, kh, d, theta, dt, batch_cs):
     assert_close(qe, hq, r, "q vs HF eager")
 
 
+def test_rope_head_major_storage_and_unsqueeze_dim_2():
+    """q/k stored [B, H, L, D] (head-major) go through the strided path; unsqueeze_dim=2 means the caller's
+    tensors are [B, L, H, D]."""
+    gen = g(31)
+    b, l, qh, kh, d = 2, 33, 6, 2, 64
+    q = torch.randn(b, qh, l, d, generator=gen).to(torch.bfloat16); k = torch.randn(b, kh, l, d, generator=gen).to(torch.bfloat16)
+    cos, sin = E.rope_cos_sin(torch.arange(l)[None], d, 1e4, torch.bfloat16)
+    qo, ko = E.rope_fwd(q, k, cos, sin)
+    qd, kd = q.to(DEV).contiguous(), k.to(DEV).contiguous()          # head-major storage
+    q1, k1 = core.fused_apply_rope(qd, kd, cos.to(DEV), sin.to(DEV))
+    assert q1.data_ptr() == qd.data_ptr()
+    assert_close(q1, qo, 1e-2, "q"); assert_close(k1, ko, 1e-2, "k")
+    q2 = q.to(DEV).transpose(1, 2).contiguous(); k2 = k.to(DEV).transpose(1, 2).contiguous()   # [B, L, H, D]
+    q3, k3 = core.fused_apply_rope(q2, k2, cos.to(DEV), sin.to(DEV), unsqueeze_dim=2)
+    assert q3.shape == (b, l, qh, d)
+    assert_close(q3.transpose(1, 2), qo, 1e-2, "q, unsqueeze_dim=2"); assert_close(k3.transpose(1, 2), ko, 1e-2, "k, unsqueeze_dim=2")
+
+
 def test_rope_round_trip_full_size():
     """Llama-3-8B shape (8 x 4096 tokens): backward(forward(x)) == x because cos^2 + sin^2 == 1; and
     memory next to the tensors is untouched."""
