@@ -24,14 +24,16 @@ struct RowPlan {
 inline RowPlan plan_rows(int64_t nvec, int min_bt) {
   RowPlan p{0, 0, 0, 0};
   if (nvec <= 0 || nvec > 8192) return p;
-  int G = next_pow2(ceil_div(nvec, 2));
+  // two vectors per thread; G a power of two (a group of 224 threads for 448 vectors measured slower than
+  // 256 threads with idle lanes)
+  int64_t G = next_pow2(ceil_div(nvec, 2));
   if (G < 32) G = 32;
   if (G > 1024) G = 1024;
   int64_t need = ceil_div(nvec, G);
   p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
-  p.G = G;
-  p.BT = G > min_bt ? G : min_bt;
-  p.gpc = p.BT / G;
+  p.G = (int)G;
+  p.gpc = G >= min_bt ? 1 : (int)(min_bt / G);
+  p.BT = p.G * p.gpc;
   return p;
 }
 

@@ -509,3 +509,43 @@ def test_direct_c_abi_calls_with_strides():
     lo, so = E.vp_combine(stats.cpu(), lb2.cpu())
     assert torch.allclose(l_out.cpu(), lo, atol=1e-5) and torch.allclose(s_out.cpu(), so, atol=1e-5)
     assert _C.launch_count() > 0
+
+
+def test_entry_points_are_cuda_graph_capturable():
+    """The C-ABI calls enqueue work only: capturing them on a side stream into a CUDA graph and replaying
+    the graph must reproduce the eager results (includes the cluster launch of the one-pass cross-entropy)."""
+    lib = _C.lib()
+    gen = torch.Generator(DEV).manual_seed(5)
+    M, N, V = 256, 2048, 32000
+    bf = _C.MDY_BF16
+    x = torch.randn(M, N, device=DEV, dtype=torch.bfloat16, generator=gen); w = torch.ones(N, device=DEV, dtype=torch.bfloat16)
+    y = torch.empty_like(x); rstd = torch.empty(M, device=DEV)
+    up = torch.randn(M, N, device=DEV, dtype=torch.bfloat16, generator=gen); sy = torch.empty_like(up)
+    lg = torch.randn(M, V, device=DEV, dtype=torch.bfloat16, generator=gen); dlg = torch.empty_like(lg)
+    lb = torch.randint(0, V, (M,), device=DEV, generator=gen)
+    losses = torch.empty(M, device=DEV); lse = torch.empty(M, device=DEV); inv = torch.tensor([1.0 / M], device=DEV)
+
+    def enqueue(stream):
+        st = stream.cuda_stream
+        _C.check(lib.mdy_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), M, N, N, N, 1e-6, bf, bf, st), "n")
+        _C.check(lib.mdy_swiglu_fwd(up.data_ptr(), x.data_ptr(), sy.data_ptr(), M, N, N, N, N, bf, st), "s")
+        _C.check(lib.mdy_ce_fused(lg.data_ptr(), dlg.data_ptr(), lb.data_ptr(), losses.data_ptr(), lse.data_ptr(), inv.data_ptr(), 1.0,
+                                  M, V, V, bf, st), "c")
+
+    enqueue(torch.cuda.current_stream())          # eager (also performs one-time set-up outside capture)
+    torch.cuda.synchronize()
+    ref = [t.clone() for t in (y, sy, dlg, losses)]
+    for t in (y, sy, dlg, losses):
+        t.zero_()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            enqueue(side)
+    torch.cuda.synchronize()
+    assert all(float(t.float().abs().sum()) == 0 for t in (y, sy, losses))   # capture did not execute
+    graph.replay()
+    torch.cuda.synchronize()
+    for got, want in zip((y, sy, dlg, losses), ref):
+        assert torch.equal(got, want)
