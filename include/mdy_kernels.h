@@ -72,7 +72,9 @@ const char* mdy_status_string(int status);
 #define MDY_TUNE_ROPE_HEADS_PER_THREAD 10 /* heads a RoPE thread rotates per work item: 1, 2 or 4       */
 #define MDY_TUNE_ROPE_GRID_PER_SM 11      /* cap of the RoPE grid, in CTAs per SM (grid-stride loop)       */
 #define MDY_TUNE_NORM_BWD_THREADS 12      /* smallest CTA of the norm backward kernels: 128, 256 or 512    */
-#define MDY_TUNE_COUNT 13
+#define MDY_TUNE_NORM_FWD_VPT 13          /* 16-byte vectors per thread the norm forward plans for: 1, 2, 4 */
+#define MDY_TUNE_NORM_BWD_VPT 14          /* the same for the norm backward                                 */
+#define MDY_TUNE_COUNT 15
 int mdy_set_tunable(int id, int value);
 /* Kernels that wait on hardware barriers bound every wait; if one ever expires they record a non-zero
  * code in a device flag and run to completion with a wrong result instead of hanging.  This call

@@ -21,12 +21,13 @@ struct RowPlan {
   int gpc;   // rows (groups) per CTA
 };
 
-inline RowPlan plan_rows(int64_t nvec, int min_bt) {
+inline RowPlan plan_rows(int64_t nvec, int min_bt, int pref_vpt = 2) {
   RowPlan p{0, 0, 0, 0};
   if (nvec <= 0 || nvec > 8192) return p;
   // two vectors per thread; G a power of two (a group of 224 threads for 448 vectors measured slower than
   // 256 threads with idle lanes)
-  int64_t G = next_pow2(ceil_div(nvec, 2));
+  if (pref_vpt != 1 && pref_vpt != 4) pref_vpt = 2;
+  int64_t G = next_pow2(ceil_div(nvec, pref_vpt));
   if (G < 32) G = 32;
   if (G > 1024) G = 1024;
   int64_t need = ceil_div(nvec, G);
@@ -86,19 +87,28 @@ norm_fwd_vec(const T* __restrict__ x, const T* __restrict__ res, const void* __r
     for (int e = 0; e < VE; ++e) wf[i][e] = v < nvec ? load_w(w, (int64_t)v * VE + e, w_dtype) : 0.f;
   }
 
-  int it = 0;
-  for (int64_t base = (int64_t)blockIdx.x * gpc; base < M; base += (int64_t)gridDim.x * gpc, ++it) {
-    const int64_t row = base + gid;
+  // Software pipeline (CTAs of up to 512 threads): the next row's loads are issued before the current
+  // row's reduction and stores, so read requests stay in flight across the barrier.
+  constexpr bool PF = MAXT <= 512 && !ADD;   // the add variant already has four streams in flight
+  const int64_t step = (int64_t)gridDim.x * gpc;
+  uint4 xv[VPT], rv[ADD ? VPT : 1];
+  uint4 nx[VPT], nr[ADD ? VPT : 1];
+  auto fetch = [&](int64_t row, uint4* px, uint4* pr) {
     const bool valid = row < M;
-    uint4 xv[VPT];
-    uint4 rv[ADD ? VPT : 1];
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
       const int v = t + i * G;
       const bool on = valid && v < nvec;
-      xv[i] = on ? ld_stream(x + row * x_rs + (int64_t)v * VE) : make_uint4(0, 0, 0, 0);
-      if (ADD) rv[i] = on ? ld_stream(res + row * res_rs + (int64_t)v * VE) : make_uint4(0, 0, 0, 0);
+      px[i] = on ? ld_stream(x + row * x_rs + (int64_t)v * VE) : make_uint4(0, 0, 0, 0);
+      if (ADD) pr[i] = on ? ld_stream(res + row * res_rs + (int64_t)v * VE) : make_uint4(0, 0, 0, 0);
     }
+  };
+  fetch((int64_t)blockIdx.x * gpc + gid, xv, rv);
+  int it = 0;
+  for (int64_t base = (int64_t)blockIdx.x * gpc; base < M; base += step, ++it) {
+    const int64_t row = base + gid;
+    const bool valid = row < M;
+    if (PF && base + step < M) fetch(row + step, nx, nr);
     float f[VPT][VE];
     float ss = 0.f;
 #pragma unroll
@@ -125,6 +135,15 @@ norm_fwd_vec(const T* __restrict__ x, const T* __restrict__ res, const void* __r
       if (valid && v < nvec) st_plain(y + row * y_rs + (int64_t)v * VE, pack<T>(f[i]));
     }
     if (valid && t == 0) rstd_out[row] = rstd;
+    if (PF) {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        xv[i] = nx[i];
+        if (ADD) rv[i] = nr[i];
+      }
+    } else if (base + step < M) {
+      fetch(row + step, xv, rv);
+    }
   }
 }
 
@@ -356,7 +375,7 @@ dw_reduce(const float* __restrict__ partial, T* __restrict__ dw, int P, int64_t 
 
 inline int norm_ctas_per_sm() {
   int v = tunable(MDY_TUNE_NORM_CTAS_PER_SM);
-  return v > 0 ? v : 4;
+  return v > 0 ? v : 2;   // x (1024 / CTA threads) CTAs per SM: 8 CTAs of 256 threads measured best
 }
 
 inline int64_t vec_grid(int64_t M, const RowPlan& p, int per_sm_scale) {
@@ -392,7 +411,7 @@ inline int64_t partial_rows(int64_t M, int64_t N) {
   constexpr int VE = VecInfo<T>::kElems;
   int64_t rows = scalar_grid(M);
   if (N % VE == 0) {
-    RowPlan p = plan_rows(N / VE, bwd_min_threads());
+    RowPlan p = plan_rows(N / VE, bwd_min_threads(), tunable(MDY_TUNE_NORM_BWD_VPT));
     if (p.vpt) {
       int64_t g = vec_grid(M, p, bwd_per_sm(p));
       if (g > rows) rows = g;
@@ -410,7 +429,7 @@ int launch_fwd(const void* x_, const void* res_, const void* w, int w_dtype, voi
   T* y = (T*)y_; T* nres = (T*)nres_;
   bool vec = N % VE == 0 && aligned16(x) && aligned16(y) && x_rs % VE == 0 && y_rs % VE == 0;
   if (ADD) vec = vec && aligned16(res) && aligned16(nres) && res_rs % VE == 0 && nres_rs % VE == 0;
-  RowPlan p = vec ? plan_rows(N / VE, 256) : RowPlan{0, 0, 0, 0};
+  RowPlan p = vec ? plan_rows(N / VE, 256, tunable(MDY_TUNE_NORM_FWD_VPT)) : RowPlan{0, 0, 0, 0};
   if (p.vpt) {
     const int64_t grid = vec_grid(M, p, norm_ctas_per_sm() * (1024 / p.BT));
     const size_t sh = 2 * (p.BT / 32) * sizeof(float);
@@ -421,7 +440,7 @@ int launch_fwd(const void* x_, const void* res_, const void* w, int w_dtype, voi
                                                                 M, (int)N, x_rs, res_rs, y_rs,   \
                                                                 nres_rs, eps, p.G)
     if (p.BT <= 512) {
-      if (p.vpt == 1) MDY_FWD(1, 512); else MDY_FWD(2, 512);
+      if (p.vpt == 1) MDY_FWD(1, 512); else if (p.vpt == 2) MDY_FWD(2, 512); else MDY_FWD(4, 512);
     } else {
       switch (p.vpt) {
         case 1: case 2: MDY_FWD(2, 1024); break;
@@ -447,7 +466,7 @@ int launch_bwd(const void* dy_, const void* x_, const void* w, int w_dtype, cons
   bool vec = N % VE == 0 && aligned16(dy) && aligned16(x) && aligned16(dx) && dy_rs % VE == 0 &&
              x_rs % VE == 0 && dx_rs % VE == 0;
   if (ADD && dres) vec = vec && aligned16(dres) && dres_rs % VE == 0;
-  RowPlan p = vec ? plan_rows(N / VE, bwd_min_threads()) : RowPlan{0, 0, 0, 0};
+  RowPlan p = vec ? plan_rows(N / VE, bwd_min_threads(), tunable(MDY_TUNE_NORM_BWD_VPT)) : RowPlan{0, 0, 0, 0};
   int64_t grid;
   if (M == 0) {
     grid = 0;  // nothing to sweep: the reduce below writes dw = 0
@@ -459,7 +478,7 @@ int launch_bwd(const void* dy_, const void* x_, const void* w, int w_dtype, cons
                                                                 dx, dw_partial, M, (int)N,      \
                                                                 dy_rs, x_rs, dres_rs, dx_rs, p.G)
     if (p.BT <= 512) {
-      if (p.vpt == 1) MDY_BWD(1, 512); else MDY_BWD(2, 512);
+      if (p.vpt == 1) MDY_BWD(1, 512); else if (p.vpt == 2) MDY_BWD(2, 512); else MDY_BWD(4, 512);
     } else {
       switch (p.vpt) {
         case 1: case 2: MDY_BWD(2, 1024); break;

@@ -549,3 +549,17 @@ def test_entry_points_are_cuda_graph_capturable():
     torch.cuda.synchronize()
     for got, want in zip((y, sy, dlg, losses), ref):
         assert torch.equal(got, want)
+
+
+def test_megatron_swiglu_adapter():
+    from mdy_triton_b200.core.megatron import swiglu_impl
+    gen = g(41)
+    x = torch.randn(3, 16, 2 * 256, generator=gen).to(torch.bfloat16); b = torch.randn(2 * 256, generator=gen).to(torch.bfloat16)
+    xd = leaf(x)
+    y = swiglu_impl(xd, b.to(DEV)); y.float().sum().backward()
+    xb = (x.float() + b.float()).to(torch.bfloat16)
+    up, gate = E.split_no_split(xb, "gate-up")
+    assert_close(y, E.swiglu_fwd(up, gate), 1e-2, "y")
+    du, dg = E.swiglu_bwd(torch.ones(3, 16, 256), up, gate)
+    gu, gg = E.split_no_split(xd.grad, "gate-up")
+    assert_close(gu, du, 1e-2, "dup"); assert_close(gg, dg, 1e-2, "dgate")
