@@ -37,7 +37,9 @@ __device__ __forceinline__ void rotate(float& a, float& b, float c1, float c2, f
   }
 }
 
-template <typename T, bool BWD, int HPT>
+// IDX is the type of the flat work-item index: uint32_t whenever the item count fits (the usual case;
+// 32-bit divisions cost a fraction of the emulated 64-bit ones and this kernel is issue-bound), else int64_t.
+template <typename T, bool BWD, int HPT, typename IDX>
 __global__ void __launch_bounds__(256)
 rope_vec(RopeArgs a) {
   constexpr int VE = VecInfo<T>::kElems;
@@ -45,19 +47,18 @@ rope_vec(RopeArgs a) {
   const int hv = half / VE;                      // vectors per half head
   const int H = a.QH + a.KH;
   const int nchunk = (H + HPT - 1) / HPT;
-  const int64_t per_tok = (int64_t)hv * nchunk;
-  const int64_t total = (int64_t)a.B * a.L * per_tok;
+  const IDX per_tok = (IDX)hv * (IDX)nchunk;
+  const IDX total = (IDX)a.B * (IDX)a.L * per_tok;
   const T* cosp = (const T*)a.cos;
   const T* sinp = (const T*)a.sin;
 
-  for (int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t tok = idx / per_tok;
+  for (IDX idx = (IDX)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (IDX)gridDim.x * blockDim.x) {
+    const IDX tok = idx / per_tok;
     const int rem = (int)(idx - tok * per_tok);
-    const int chunk = rem / hv;
+    const int chunk = (int)((unsigned)rem / (unsigned)hv);
     const int j = rem - chunk * hv;
-    const int b = (int)(tok / a.L);
-    const int l = (int)(tok - (int64_t)b * a.L);
+    const int b = (int)(tok / (IDX)a.L);
+    const int l = (int)(tok - (IDX)b * (IDX)a.L);
 
     const int64_t cs_off = (int64_t)b * a.cos_sb + (int64_t)l * a.D + (int64_t)j * VE;
     const uint4 c1v = ld_reuse(cosp + cs_off);
@@ -168,8 +169,15 @@ int launch_rope_h(const RopeArgs& a, bool bwd, cudaStream_t st) {
   const int64_t cap = (int64_t)(num_sms() > 0 ? num_sms() : 1) * waves;
   if (grid > cap) grid = cap;
   if (vec) {
-    if (bwd) rope_vec<T, true, HPT><<<(unsigned)grid, threads, 0, st>>>(a);
-    else rope_vec<T, false, HPT><<<(unsigned)grid, threads, 0, st>>>(a);
+    // the grid-stride loop adds at most grid*threads to an index below `items`
+    const bool small = items + grid * threads < ((int64_t)1 << 32);
+    if (small) {
+      if (bwd) rope_vec<T, true, HPT, uint32_t><<<(unsigned)grid, threads, 0, st>>>(a);
+      else rope_vec<T, false, HPT, uint32_t><<<(unsigned)grid, threads, 0, st>>>(a);
+    } else {
+      if (bwd) rope_vec<T, true, HPT, int64_t><<<(unsigned)grid, threads, 0, st>>>(a);
+      else rope_vec<T, false, HPT, int64_t><<<(unsigned)grid, threads, 0, st>>>(a);
+    }
   } else {
     if (bwd) rope_scalar<T, true><<<(unsigned)grid, threads, 0, st>>>(a);
     else rope_scalar<T, false><<<(unsigned)grid, threads, 0, st>>>(a);
