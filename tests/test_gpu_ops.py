@@ -563,3 +563,47 @@ def test_megatron_swiglu_adapter():
     du, dg = E.swiglu_bwd(torch.ones(3, 16, 256), up, gate)
     gu, gg = E.split_no_split(xd.grad, "gate-up")
     assert_close(gu, du, 1e-2, "dup"); assert_close(gg, dg, 1e-2, "dgate")
+
+
+def test_operators_on_a_side_stream_and_from_threads():
+    """Entry points enqueue on the caller's current stream and keep no per-call host state, so calls from
+    several Python threads, each on its own stream, give the same results as serial calls."""
+    import threading
+    gen = g(51)
+    xs = [torch.randn(512, 1024, generator=gen).to(torch.bfloat16).to(DEV) for _ in range(4)]
+    w = torch.ones(1024, dtype=torch.bfloat16, device=DEV)
+    want = [core.triton_rmsnorm(x, w, 1e-6) for x in xs]
+    torch.cuda.synchronize()
+    got = [None] * 4
+
+    def work(i):
+        s = torch.cuda.Stream()
+        with torch.cuda.stream(s):
+            y = core.triton_fused_up_gate_silu(xs[i], xs[i])          # two different operators per thread
+            got[i] = (core.triton_rmsnorm(xs[i], w, 1e-6), y)
+        s.synchronize()
+
+    ts = [threading.Thread(target=work, args=(i,)) for i in range(4)]
+    for t in ts:
+        t.start()
+    for t in ts:
+        t.join()
+    for i in range(4):
+        assert torch.equal(got[i][0], want[i])
+        assert_close(got[i][1], E.swiglu_fwd(xs[i].cpu(), xs[i].cpu()), 1e-2)
+
+
+def test_operators_follow_the_tensor_device_not_the_current_device():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    gen = g(52)
+    x = torch.randn(64, 512, generator=gen).to(torch.bfloat16)
+    w = torch.ones(512, dtype=torch.bfloat16)
+    with torch.cuda.device(0):
+        y1 = core.triton_rmsnorm(x.to("cuda:1"), w.to("cuda:1"), 1e-6)      # current device 0, tensors on 1
+        lg = torch.randn(8, 32000, generator=gen).to(torch.bfloat16).to("cuda:1").requires_grad_(True)
+        loss = triton_entropy_loss(lg, torch.randint(0, 32000, (8,), generator=gen).to("cuda:1"))
+        loss.backward()
+    assert y1.device.index == 1 and lg.grad.device.index == 1
+    assert_close(y1, E.rmsnorm_fwd(x, w, 1e-6)[0], 1e-2)
+    assert torch.isfinite(lg.grad).all()
