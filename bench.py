@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c1|c2|c3]
 
-One step = forward + backward of the fused operator set at one BASELINE config (default c2, the
+One step = forward + backward of the fused operator set at one benchmark config (default c2, the
 Llama-3-8B-shaped set: add+RMSNorm [32768,4096], RoPE 32q/8kv heads x 128, SwiGLU [32768,14336],
 cross-entropy [32768,128256], bf16) on synthetic seeded inputs.  Every rank owns its own 32768-token
 shard (tokens are independent: no data-path collective), so the job is weak-scaled.
@@ -369,7 +369,7 @@ def run_cpu_baseline(cfg, tokens, steps, warmup, seed):
 
 # ------------------------------------------------------------------------------------ Llama-1B train step
 def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, seq=4096):
-    """BASELINE config 4: random-init Llama-style 1B decoder (16 layers, hidden 2048, 32 q / 8 kv heads,
+    """Training-step workload: random-init Llama-style 1B decoder (16 layers, hidden 2048, 32 q / 8 kv heads,
     head_dim 64, FFN 8192, vocab 128256, eps 1e-5, theta 5e5), bf16 parameters with float32 master weights
     and AdamW state, full forward+backward+optimizer step, synthetic tokens uniform in the vocabulary,
     micro-batch 4 x 4096 per GPU, DDP gradient all-reduce over NCCL when world > 1.  Returns a dict."""
@@ -438,7 +438,7 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
 
 # ------------------------------------------------------------------------------ vocab-parallel CE sweep
 def run_vpce(dev, dist, world, rank, steps, warmup):
-    """BASELINE config 5: 16384 tokens, vocab in {32000, 128256, 151936, 256000} sharded over the ranks,
+    """Vocab-parallel sweep: 16384 tokens, vocab in {32000, 128256, 151936, 256000} sharded over the ranks,
     logits N(0, sigma^2) with sigma in {1, 4}, 5 % of the labels -100, bf16, gradient written in place.
     Per step and rank: local sweep (mdy_ce_fwd, split mode) -> one all_gather of [2, M] float32 ->
     mdy_ce_vp_combine -> local gradient sweep (mdy_ce_bwd).  The collective is inside the timed region."""

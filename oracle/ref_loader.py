@@ -2,7 +2,7 @@
 
 The reference package cannot be imported as a package (its ``core/__init__.py`` imports a name its
 loss module no longer defines), so each kernel file is loaded by path from a reference checkout
-(default ``/root/reference``, override with ``MDY_REFERENCE_ROOT``).  Nothing is copied into this
+(its path comes from ``MDY_REFERENCE_ROOT``; the default is the checkout's usual mount point).  Nothing is copied into this
 repository: a patched copy of each file is written to a temporary directory because Triton's JIT needs
 a source file, with only these host-side shims, none of which touches kernel arithmetic:
 

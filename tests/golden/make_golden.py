@@ -2,7 +2,7 @@
 
     TRITON_INTERPRET=1 python tests/golden/make_golden.py
 
-Needs a reference checkout (``oracle/ref_loader.py``: default /root/reference).  Each case stores its
+Needs a reference checkout (located by ``oracle/ref_loader.py``, ``MDY_REFERENCE_ROOT``).  Each case stores its
 seeded inputs and the outputs / gradients the reference operator produced for them when run on CPU
 under Triton's interpreter.  The files are small on purpose; they travel with the repository to
 machines that have no reference checkout.

@@ -118,7 +118,7 @@ def test_rank_failing_before_the_collective_is_reported_not_hung():
                                            (151936, 4, 1.0, torch.bfloat16), (256000, 8, 4.0, torch.bfloat16),
                                            (1500, 4, 1.0, torch.float32)])
 def test_kernels_over_all_shards_on_one_gpu(v, tp, sigma, dt):
-    """The vocab-parallel sweep of BASELINE config 5 at reduced token count: every rank's local forward,
+    """The vocab-parallel sweep (four vocabularies, two logit scales) at reduced token count: every rank's local forward,
     the combine kernel and every rank's local backward, run one after the other on a single device."""
     from mdy_triton_b200.core import vocab_parallel as vp
     dev = torch.device("cuda", 0)
