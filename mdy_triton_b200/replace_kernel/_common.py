@@ -121,9 +121,10 @@ def make_causal_forward(original_forward, output_cls=CausalLMOutputWithPast, ext
     params = inspect.signature(original_forward).parameters
     keep_name = "logits_to_keep" if "logits_to_keep" in params else "num_logits_to_keep"
 
-    def causal_forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
-                       inputs_embeds=None, labels=None, use_cache=None, **kwargs):
-        keep = kwargs.pop(keep_name, 0)
+    def _forward(self, input_ids, attention_mask, position_ids, past_key_values, inputs_embeds, labels, use_cache,
+                 keep, kwargs):
+        if keep is None:
+            keep = 0
         n_items = kwargs.pop("num_items_in_batch", None) or kwargs.pop("n_items", None)
         shift = kwargs.pop("shift_labels", None)
         outputs = self.model(input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
@@ -147,6 +148,19 @@ def make_causal_forward(original_forward, output_cls=CausalLMOutputWithPast, ext
                           past_key_values=getattr(outputs, "past_key_values", None),
                           hidden_states=getattr(outputs, "hidden_states", None),
                           attentions=getattr(outputs, "attentions", None), **extra)
+
+    # The keep-last-logits argument is an explicit parameter under the installed transformers' name:
+    # `generate` inspects the signature to decide whether it may ask for the last position only.
+    if keep_name == "logits_to_keep":
+        def causal_forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
+                           inputs_embeds=None, labels=None, use_cache=None, logits_to_keep=0, **kwargs):
+            return _forward(self, input_ids, attention_mask, position_ids, past_key_values, inputs_embeds, labels,
+                            use_cache, logits_to_keep, kwargs)
+    else:  # pragma: no cover - older transformers
+        def causal_forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None,
+                           inputs_embeds=None, labels=None, use_cache=None, num_logits_to_keep=0, **kwargs):
+            return _forward(self, input_ids, attention_mask, position_ids, past_key_values, inputs_embeds, labels,
+                            use_cache, num_logits_to_keep, kwargs)
 
     causal_forward.__doc__ = make_causal_forward.__doc__
     return can_return_tuple(causal_forward)

@@ -20,6 +20,7 @@ def _check_family(modname, prefix, rope=True):
     lm = getattr(m, prefix + "ForCausalLM").forward
     assert dec.__module__ == _common.__name__
     assert "labels" in inspect.signature(lm).parameters
+    assert "logits_to_keep" in inspect.signature(lm).parameters   # generate() looks for it by name
     assert "hidden_states" in inspect.signature(dec).parameters
     return m
 
