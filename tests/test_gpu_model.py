@@ -23,11 +23,18 @@ import transformers
 cfg_cls, model_cls = {{"llama": (transformers.LlamaConfig, transformers.LlamaForCausalLM),
                       "qwen2": (transformers.Qwen2Config, transformers.Qwen2ForCausalLM),
                       "mistral": (transformers.MistralConfig, transformers.MistralForCausalLM),
-                      "phi3": (transformers.Phi3Config, transformers.Phi3ForCausalLM)}}[family]
+                      "phi3": (transformers.Phi3Config, transformers.Phi3ForCausalLM),
+                      "qwen2_vl": (transformers.Qwen2VLConfig, transformers.Qwen2VLForConditionalGeneration)}}[family]
 extra = {{"pad_token_id": 0}} if family == "phi3" else {{}}
-cfg = cfg_cls(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
-              vocab_size=2048, max_position_embeddings=128, rms_norm_eps=1e-5, attn_implementation="sdpa",
-              tie_word_embeddings=False, **extra)
+text = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+            vocab_size=2048, max_position_embeddings=128, rms_norm_eps=1e-5, tie_word_embeddings=False, **extra)
+if family == "qwen2_vl":
+    text["rope_scaling"] = {{"type": "mrope", "mrope_section": [8, 12, 12]}}
+    cfg = cfg_cls(text_config=text, attn_implementation="sdpa",
+                  vision_config=dict(depth=1, embed_dim=32, hidden_size=256, num_heads=2, mlp_ratio=2, patch_size=14,
+                                     spatial_merge_size=2, temporal_patch_size=2))
+else:
+    cfg = cfg_cls(attn_implementation="sdpa", **text)
 torch.manual_seed(0)
 model = model_cls(cfg).to("cuda").to(dtype)
 g = torch.Generator().manual_seed(1)
@@ -36,7 +43,7 @@ labels = ids.clone(); labels[0, :10] = -100
 out = model(input_ids=ids, labels=labels)
 out.loss.backward()
 res = {{"loss": float(out.loss), "logits_shape": list(out.logits.shape)}}
-params = dict(model.named_parameters())
+params = {{k.replace("model.language_model.", "model."): v for k, v in model.named_parameters()}}
 for name in ("model.embed_tokens.weight", "model.layers.0.input_layernorm.weight", "model.layers.1.post_attention_layernorm.weight",
              "model.layers.0.self_attn.q_proj.weight", "model.layers.0.self_attn.qkv_proj.weight", "model.layers.1.mlp.gate_proj.weight",
              "model.layers.1.mlp.gate_up_proj.weight", "model.norm.weight", "lm_head.weight"):
@@ -60,7 +67,7 @@ def _run(family, patched, dtype):
     return json.loads(line[7:])
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen2", "mistral", "phi3"])
+@pytest.mark.parametrize("family", ["llama", "qwen2", "mistral", "phi3", "qwen2_vl"])
 def test_patched_model_matches_stock_model_fp32(family):
     a = _run(family, False, "float32")
     b = _run(family, True, "float32")
