@@ -65,8 +65,9 @@ const char* mdy_status_string(int status);
                                         4 cluster kernel caching the exponentials in shared memory */
 #define MDY_TUNE_ROPE_THREADS 5      /* threads per CTA of the RoPE kernel                         */
 #define MDY_TUNE_CE_CLUSTER_SLICE_KB 6 /* largest slice of a row one CTA of the cluster kernel stages (KiB) */
-#define MDY_TUNE_CE_CLUSTER_THREADS 7  /* threads per CTA of the cluster kernel: 512 or 1024          */
-#define MDY_TUNE_CE_CLUSTER_VPC 8      /* 16-byte vectors per thread per chunk there: 1, 2 or 4       */
+#define MDY_TUNE_CE_CLUSTER_THREADS 7  /* threads per CTA of the cluster kernel; with ids 8 and 15 selects a compiled shape:
+                                          (threads, vectors, CTAs/SM) = (256,4,3) (256,8,2) (512,2,2) (512,4,1) (1024,2,1) */
+#define MDY_TUNE_CE_CLUSTER_VPC 8      /* 16-byte vectors per thread per chunk there */
 #define MDY_TUNE_CE_REG_SHAPE 9        /* impl 3: 0/3 = 512 threads x 8 vectors, 1 = 256x8, 2 = 512x4, 4 = 1024x4;
                                           impl 4 / auto: 0 = smallest CTA that fits, 1 = 512, 2 = 1024 threads */
 #define MDY_TUNE_ROPE_HEADS_PER_THREAD 10 /* heads a RoPE thread rotates per work item: 1, 2 or 4       */
@@ -74,7 +75,8 @@ const char* mdy_status_string(int status);
 #define MDY_TUNE_NORM_BWD_THREADS 12      /* smallest CTA of the norm backward kernels: 128, 256 or 512    */
 #define MDY_TUNE_NORM_FWD_VPT 13          /* 16-byte vectors per thread the norm forward plans for: 1, 2, 4 */
 #define MDY_TUNE_NORM_BWD_VPT 14          /* the same for the norm backward                                 */
-#define MDY_TUNE_COUNT 15
+#define MDY_TUNE_CE_CLUSTER_MINB 15        /* CTAs per SM that shape is compiled for (register cap)                 */
+#define MDY_TUNE_COUNT 16
 int mdy_set_tunable(int id, int value);
 /* Kernels that wait on hardware barriers bound every wait; if one ever expires they record a non-zero
  * code in a device flag and run to completion with a wrong result instead of hanging.  This call

@@ -33,6 +33,7 @@ TUNE_ROPE_GRID_PER_SM = 11
 TUNE_NORM_BWD_THREADS = 12
 TUNE_NORM_FWD_VPT = 13
 TUNE_NORM_BWD_VPT = 14
+TUNE_CE_CLUSTER_MINB = 15
 
 _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 

@@ -142,6 +142,19 @@ __device__ __forceinline__ void merge_nb(float& m, float& s, float om, float os)
   m = fmaxf(m, om);
 }
 
+// (max, sum-exp) over groups of W adjacent lanes, left in every lane of the group: a max butterfly, ONE
+// rescale per lane, a sum butterfly (a shorter dependency chain than log2(W) merges with an exp each).
+template <int W>
+__device__ __forceinline__ void group_merge(float& m, float& s) {
+  float gm = m;
+#pragma unroll
+  for (int o = W / 2; o > 0; o >>= 1) gm = fmaxf(gm, __shfl_xor_sync(0xffffffffu, gm, o));
+  s *= fast_exp2((fmaxf(m, -1e37f) - fmaxf(gm, -1e37f)) * kLog2e);  // an empty lane's s == 0 stays 0
+#pragma unroll
+  for (int o = W / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+  m = gm;
+}
+
 // Sweep-1 work on VPC vectors already in registers: one max/rescale per call, then 8*VPC exps
 // accumulated in two independent sums.
 template <typename T, int VPC>
@@ -238,9 +251,10 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
   const uint32_t my_s = slice_s + (uint32_t)tid * 16u;
 #ifdef MDY_CE_TIMING
   long long tacc[6] = {0, 0, 0, 0, 0, 0};
+  long long twait[4] = {0, 0, 0, 0};
   long long tlast = clock64();
 #endif
-  // labels are fetched one row ahead, so the global load is never on the row's critical path
+  // labels are fetched two rows ahead, so the global load is never on the row's critical path
   int64_t label_after = MDY_IGNORE_INDEX;
   int64_t label = row < a.M ? a.labels[row] : MDY_IGNORE_INDEX;
   int64_t label_next = row + ncl < a.M ? a.labels[row + ncl] : MDY_IGNORE_INDEX;
@@ -248,11 +262,11 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
     const bool cur_valid = label != MDY_IGNORE_INDEX;
     const int64_t nrow = row + ncl;
     const bool next_valid = nrow < a.M && label_next != MDY_IGNORE_INDEX;
-    label_after = nrow + ncl < a.M ? a.labels[nrow + ncl] : MDY_IGNORE_INDEX;
     T* dst = dlogits + row * a.rs + (int64_t)slice_elem0 + (int64_t)tid * VE;
 
     if (!cur_valid) {
       // ignored row: nothing was loaded; zero-fill the slice and start fetching the next row
+      label_after = nrow + ncl < a.M ? a.labels[nrow + ncl] : MDY_IGNORE_INDEX;
       if (crank == 0 && tid == 0) { a.losses[row] = 0.f; a.lse[row] = 0.f; }
       if (tid == 0 && next_valid) {
         for (int k = 0; k < nchunk; ++k) issue_chunk(nrow, k);
@@ -267,7 +281,13 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
     const uint32_t parity = nloaded & 1u;
     float m = -INFINITY, s0 = 0.f, s1 = 0.f;
     for (int k = 0; k < nfull; ++k) {
+#ifdef MDY_CE_TIMING
+      const long long tw_ = clock64();
+#endif
       mbar_wait(full_s + 8 * k, parity, dead);
+#ifdef MDY_CE_TIMING
+      if (nloaded > 0) twait[k < 4 ? k : 3] += clock64() - tw_;  // the first row's wait is the cold-start latency
+#endif
       uint4 q[VPC];
 #pragma unroll
       for (int j = 0; j < VPC; ++j) q[j] = lds128(my_s + (uint32_t)(k * CV + j * NT) * 16u);
@@ -285,12 +305,7 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
     }
     MDY_TICK(1)
     float s = s0 + s1;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float om = __shfl_xor_sync(0xffffffffu, m, o);
-      const float os = __shfl_xor_sync(0xffffffffu, s, o);
-      merge_nb(m, s, om, os);
-    }
+    group_merge<32>(m, s);
     if (lane == 0) { red[warp] = m; red[32 + warp] = s; }
     __syncthreads();
     MDY_TICK(2)
@@ -302,12 +317,7 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
     if (warp == 0) {
       m = lane < NW ? red[lane] : -INFINITY;
       s = lane < NW ? red[32 + lane] : 0.f;
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        const float om = __shfl_xor_sync(0xffffffffu, m, o);
-        const float os = __shfl_xor_sync(0xffffffffu, s, o);
-        merge_nb(m, s, om, os);
-      }
+      group_merge<(NW <= 8 ? 8 : NW <= 16 ? 16 : 32)>(m, s);
       if (lane == 0) {
         // (max, sum, label logit) to every CTA of the cluster, itself included: 16 bytes that complete
         // 16 tx bytes on the receiver's exchange barrier (no cluster-wide barrier or fence per row)
@@ -336,6 +346,9 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
       a.lse[row] = lse;
     }
     ++nloaded;
+    // the label two rows ahead is fetched here: a global load in flight when sweep 1 polls its chunk
+    // barriers was measured to delay those polls by its whole latency
+    label_after = nrow + ncl < a.M ? a.labels[nrow + ncl] : MDY_IGNORE_INDEX;
 
     // ---- sweep 2: gradient from the staged slice; refill each chunk as soon as it is consumed ----
     const float c2 = -lse * kLog2e + log2g;
@@ -376,12 +389,14 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
     float* o = a.lse + a.M + (blockIdx.x * 3 + (tid == 0 ? 0 : tid == 40 ? 1 : 2)) * 8;
     for (int i = 0; i < 5; ++i) o[i] = (float)tacc[i];
     o[5] = (float)nloaded;
+    o[6] = (float)(twait[0]);
+    o[7] = (float)(twait[1] + twait[2] + twait[3]);
   }
 #endif
 }
 
-template <typename T, int NT, int VPC>
-__global__ void __launch_bounds__(NT, (NT <= 512 ? 3 : 1)) ce_cluster_kernel(ClusterArgs a) {
+template <typename T, int NT, int VPC, int MINB>
+__global__ void __launch_bounds__(NT, MINB) ce_cluster_kernel(ClusterArgs a) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const uint32_t full_s = smem_u32(smem_raw + a.slice_bytes_aligned);
   if (threadIdx.x == 0) {
@@ -402,7 +417,7 @@ inline int cluster_slice_limit() {
   return kb * 1024;
 }
 
-template <typename T, int NT, int VPC>
+template <typename T, int NT, int VPC, int MINB>
 int launch_cluster_nt(ClusterArgs a, cudaStream_t st) {
   constexpr int VE = VecInfo<T>::kElems;
   const int64_t row_bytes = a.V * (int64_t)sizeof(T);
@@ -421,7 +436,7 @@ int launch_cluster_nt(ClusterArgs a, cudaStream_t st) {
   a.slice_bytes_aligned = (int)((vpc * 16 + 127) / 128 * 128);
   const size_t smem = (size_t)a.slice_bytes_aligned + (kMaxChunks + 2) * 8 + 2 * kMaxCluster * 4 * 4 + 64 * 4;
 
-  auto kern = ce_cluster_kernel<T, NT, VPC>;
+  auto kern = ce_cluster_kernel<T, NT, VPC, MINB>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
   cudaLaunchConfig_t cfg = {};
@@ -461,15 +476,19 @@ int launch_cluster(const ClusterArgs& a, cudaStream_t st) {
   if (a.V >= ((int64_t)1 << 27)) return MDY_ERR_UNSUPPORTED;
   const int nt = tunable(MDY_TUNE_CE_CLUSTER_THREADS);
   const int vpc = tunable(MDY_TUNE_CE_CLUSTER_VPC);
-  // default (measured best at V = 128256, bf16): one 1024-thread CTA per SM, 32 KB chunks
-  if (nt == 512) {
-    if (vpc == 1) return launch_cluster_nt<T, 512, 1>(a, st);
-    if (vpc == 4) return launch_cluster_nt<T, 512, 4>(a, st);
-    return launch_cluster_nt<T, 512, 2>(a, st);
-  }
-  if (vpc == 1) return launch_cluster_nt<T, 1024, 1>(a, st);
-  if (vpc == 4) return launch_cluster_nt<T, 1024, 4>(a, st);
-  return launch_cluster_nt<T, 1024, 2>(a, st);
+  int minb = tunable(MDY_TUNE_CE_CLUSTER_MINB);
+  if (minb < 1) minb = 1;
+#define MDY_CL(NT_, VPC_, MINB_) \
+  if (nt == NT_ && vpc == VPC_ && minb == MINB_) return launch_cluster_nt<T, NT_, VPC_, MINB_>(a, st);
+  MDY_CL(256, 4, 3) MDY_CL(256, 8, 2) MDY_CL(512, 2, 2) MDY_CL(512, 4, 1) MDY_CL(1024, 2, 1)
+#undef MDY_CL
+  // defaults (measured at 32768 rows, bf16).  Rows of which two or three fit in one SM's shared memory:
+  // small CTAs, several per SM, so one row's reduction and exchange overlap another row's sweeps
+  // (V = 32000: 6000 GB/s against 4360 with one large CTA).  Longer rows: one 512-thread CTA per SM with
+  // up to 128 registers per thread and 32 KB chunks (V = 128256: 6040 GB/s; 1024 threads: 5440).
+  if (a.V * (int64_t)sizeof(T) <= 112 * 1024 && tunable(MDY_TUNE_CE_CLUSTER_SLICE_KB) == 0)
+    return launch_cluster_nt<T, 256, 4, 3>(a, st);
+  return launch_cluster_nt<T, 512, 4, 1>(a, st);
 }
 
 
