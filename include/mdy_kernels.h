@@ -83,6 +83,11 @@ int mdy_set_tunable(int id, int value);
  * synchronises with the device, returns the flag (0 = no such event, -1 = the flag could not be
  * read) and resets it when clear != 0.  For tests and diagnostics; not needed on the hot path. */
 int mdy_last_device_error(int clear);
+/* Launch geometry of the calling thread's most recent cluster-kernel cross-entropy launch: CTAs per
+ * cluster, clusters launched (= co-resident clusters, or M if smaller), threads per CTA, dynamic shared
+ * memory per CTA.  Any pointer may be NULL.  Returns MDY_ERR_ARG if this thread has not launched one.
+ * For profiling notes and tests; the reference has no counterpart. */
+int mdy_ce_last_geometry(int* cluster_ctas, int* clusters, int* threads, int* smem_bytes);
 int mdy_get_tunable(int id);
 
 /* ---- RMSNorm ------------------------------------------------------------------------------ */

@@ -28,6 +28,7 @@ constexpr int kMaxChunks = 32;
 constexpr int kMaxCluster = 8;
 
 __device__ int g_dev_error = 0;
+thread_local int t_geometry[4] = {0, 0, 0, 0};  // cluster CTAs, clusters, threads, shared memory of the last launch
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
@@ -65,6 +66,19 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, bool& d
   dead = true;
   atomicExch(&g_dev_error, 1);
 }
+// Non-blocking poll: true once the phase with this parity has completed.  Issued well before its result
+// is needed, its latency (about 200 cycles, measured) overlaps other work.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 // global -> this CTA's shared memory, completion signalled on `bar` (non-multicast bulk copy)
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
@@ -86,6 +100,16 @@ __device__ __forceinline__ void st_async_v4(uint32_t local_addr, uint32_t local_
   asm volatile("st.async.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];" ::"r"(ra),
                "f"(a), "f"(b), "f"(c), "f"(d), "r"(rb)
                : "memory");
+}
+
+// Named barrier 1 as a producer/consumer pair: `named_arrive` signals without waiting, `named_sync`
+// waits until `count` threads have arrived or synced; writes made before the arrive are visible after
+// the sync.
+__device__ __forceinline__ void named_arrive(int count) {
+  asm volatile("bar.arrive 1, %0;" ::"r"(count) : "memory");
+}
+__device__ __forceinline__ void named_sync(int count) {
+  asm volatile("bar.sync 1, %0;" ::"r"(count) : "memory");
 }
 
 __device__ __forceinline__ uint4 lds128(uint32_t addr) {
@@ -248,10 +272,10 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
   // pass the cluster barrier of the row in between)
   uint32_t nloaded = 0;
   bool dead = false;
+  bool ready0 = false;  // early poll of the next row's first chunk
   const uint32_t my_s = slice_s + (uint32_t)tid * 16u;
 #ifdef MDY_CE_TIMING
   long long tacc[6] = {0, 0, 0, 0, 0, 0};
-  long long twait[4] = {0, 0, 0, 0};
   long long tlast = clock64();
 #endif
   // labels are fetched two rows ahead, so the global load is never on the row's critical path
@@ -273,6 +297,7 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
       }
       const uint4 z = make_uint4(0, 0, 0, 0);
       for (int v = tid; v < my_nvec; v += NT) st_stream(dst + (int64_t)(v - tid) * VE, z);
+      ready0 = false;
       continue;
     }
 
@@ -280,21 +305,19 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
     // ---- sweep 1: (max, sum-exp) of the slice as its chunks land ----
     const uint32_t parity = nloaded & 1u;
     float m = -INFINITY, s0 = 0.f, s1 = 0.f;
+    // every chunk barrier is polled one chunk ahead (the first one at the end of the previous row), so
+    // the poll's latency overlaps the exponentials; the blocking wait only runs if that poll failed
+    bool ready = ready0;
     for (int k = 0; k < nfull; ++k) {
-#ifdef MDY_CE_TIMING
-      const long long tw_ = clock64();
-#endif
-      mbar_wait(full_s + 8 * k, parity, dead);
-#ifdef MDY_CE_TIMING
-      if (nloaded > 0) twait[k < 4 ? k : 3] += clock64() - tw_;  // the first row's wait is the cold-start latency
-#endif
+      if (!ready) mbar_wait(full_s + 8 * k, parity, dead);
       uint4 q[VPC];
 #pragma unroll
       for (int j = 0; j < VPC; ++j) q[j] = lds128(my_s + (uint32_t)(k * CV + j * NT) * 16u);
+      ready = k + 1 < nchunk && mbar_test(full_s + 8 * (k + 1), parity);
       stats_chunk<T, VPC>(q, m, s0, s1);
     }
     if (nfull < nchunk) {
-      mbar_wait(full_s + 8 * nfull, parity, dead);
+      if (!ready) mbar_wait(full_s + 8 * nfull, parity, dead);
       uint4 q[VPC];
 #pragma unroll
       for (int j = 0; j < VPC; ++j) {
@@ -307,14 +330,15 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
     float s = s0 + s1;
     group_merge<32>(m, s);
     if (lane == 0) { red[warp] = m; red[32 + warp] = s; }
-    __syncthreads();
-    MDY_TICK(2)
     int loc = -1;  // label position inside this CTA's slice, in elements
     if (label >= 0 && label < a.V) {
       const int64_t l = label - slice_elem0;
       if (l >= 0 && l < (int64_t)my_nvec * VE) loc = (int)l;
     }
+    // warp 0 waits for every warp's partial, the others only signal and move on
     if (warp == 0) {
+      named_sync(NT);
+      MDY_TICK(2)
       m = lane < NW ? red[lane] : -INFINITY;
       s = lane < NW ? red[32 + lane] : 0.f;
       group_merge<(NW <= 8 ? 8 : NW <= 16 ? 16 : 32)>(m, s);
@@ -327,6 +351,9 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
         mbar_expect_tx(xb, (uint32_t)C * 16u);
         for (int p = 0; p < C; ++p) st_async_v4(slot, xb, (uint32_t)p, m, s, xl, 0.f);
       }
+    } else {
+      named_arrive(NT);
+      MDY_TICK(2)
     }
     // two exchange slots suffice: a peer cannot send for row n+2 before it has this CTA's message for
     // row n+1, which leaves only after the reads of row n below
@@ -382,6 +409,7 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
       const float p = fast_exp2(fmaf(xl, kLog2e, -lse * kLog2e));
       dlogits[row * a.rs + slice_elem0 + loc] = from_float<T>((p - 1.f) * g);
     }
+    ready0 = next_valid && mbar_test(full_s, nloaded & 1u);
     MDY_TICK(4)
   }
 #ifdef MDY_CE_TIMING
@@ -389,8 +417,6 @@ __device__ __forceinline__ void cluster_rows(const ClusterArgs& a, unsigned char
     float* o = a.lse + a.M + (blockIdx.x * 3 + (tid == 0 ? 0 : tid == 40 ? 1 : 2)) * 8;
     for (int i = 0; i < 5; ++i) o[i] = (float)tacc[i];
     o[5] = (float)nloaded;
-    o[6] = (float)(twait[0]);
-    o[7] = (float)(twait[1] + twait[2] + twait[3]);
   }
 #endif
 }
@@ -466,6 +492,7 @@ int launch_cluster_nt(ClusterArgs a, cudaStream_t st) {
   cfg.gridDim = dim3((unsigned)(ncl * C), 1, 1);
   e = cudaLaunchKernelEx(&cfg, kern, a);
   if (e != cudaSuccess) return (int)e;
+  t_geometry[0] = C; t_geometry[1] = (int)ncl; t_geometry[2] = NT; t_geometry[3] = (int)smem;
   return finish_launch(1);
 }
 
@@ -1111,6 +1138,15 @@ int ce_fused_cluster(const void* logits, void* dlogits, const int64_t* labels, f
 }
 
 }  // namespace mdy
+
+extern "C" int mdy_ce_last_geometry(int* cluster_ctas, int* clusters, int* threads, int* smem_bytes) {
+  if (mdy::t_geometry[0] == 0) return MDY_ERR_ARG;
+  if (cluster_ctas) *cluster_ctas = mdy::t_geometry[0];
+  if (clusters) *clusters = mdy::t_geometry[1];
+  if (threads) *threads = mdy::t_geometry[2];
+  if (smem_bytes) *smem_bytes = mdy::t_geometry[3];
+  return MDY_OK;
+}
 
 extern "C" int mdy_last_device_error(int clear) {
   int v = 0;

@@ -483,6 +483,32 @@ def test_ce_properties_full_size(fused_impl):
     assert_close(d[sl], E.ce_grad(lg[sl].cpu(), lb[sl].cpu(), lse_o, torch.tensor(1.0 / n)), 1e-2)
 
 
+def test_ce_cluster_launch_geometry():
+    """The default one-pass launch: clusters are as small as the shared memory allows, the grid is one
+    wave of co-resident clusters (or one cluster per row if there are fewer rows), and rows short
+    enough for several CTAs per SM get the small-CTA shape."""
+    import ctypes
+    lib = _C.lib()
+    sms = lib.mdy_num_sms()
+
+    def geometry(m, v, dt=torch.bfloat16):
+        x = torch.randn(m, v, device=DEV).to(dt).requires_grad_(True)
+        triton_entropy_loss(x, torch.randint(0, v, (m,), device=DEV)).backward()
+        out = [ctypes.c_int(0) for _ in range(4)]
+        _C.check(lib.mdy_ce_last_geometry(*[ctypes.byref(o) for o in out]), "geometry")
+        return tuple(o.value for o in out)
+
+    c, ncl, nt, smem = geometry(1024, 128256)          # 250 KB rows: two CTAs per row, one CTA per SM
+    assert (c, nt) == (2, 512) and ncl == sms // 2 and 125 * 1024 < smem < 132 * 1024
+    c, ncl, nt, smem = geometry(2048, 32000)           # 62.5 KB rows: one CTA per row, three per SM
+    assert (c, nt) == (1, 256) and ncl == 3 * sms and smem < 66 * 1024
+    c, ncl, nt, smem = geometry(3, 128256)             # fewer rows than co-resident clusters
+    assert (c, ncl) == (2, 3)
+    c, ncl, nt, smem = geometry(64, 128256, torch.float32)   # 501 KB rows: three CTAs per row
+    assert c == 3 and ncl <= sms // 3
+    assert lib.mdy_last_device_error(1) == 0
+
+
 def test_direct_c_abi_calls_with_strides():
     """Call the entry points directly with row strides larger than the row."""
     lib = _C.lib()
