@@ -368,7 +368,7 @@ def run_cpu_baseline(cfg, tokens, steps, warmup, seed):
 
 
 # ------------------------------------------------------------------------------------ Llama-1B train step
-def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, seq=4096):
+def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, seq=4096, fuse_residual=False):
     """Training-step workload: random-init Llama-style 1B decoder (16 layers, hidden 2048, 32 q / 8 kv heads,
     head_dim 64, FFN 8192, vocab 128256, eps 1e-5, theta 5e5), bf16 parameters with float32 master weights
     and AdamW state, full forward+backward+optimizer step, synthetic tokens uniform in the vocabulary,
@@ -376,6 +376,7 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
     import torch.nn as nn
     if patched:
         import mdy_triton.replace_kernel  # noqa: F401  (the import is the patch)
+        mdy_triton.replace_kernel.set_residual_fusion(fuse_residual)
     from transformers import LlamaConfig, LlamaForCausalLM
     from mdy_triton_b200 import _C
     cfg = LlamaConfig(hidden_size=2048, intermediate_size=8192, num_hidden_layers=16, num_attention_heads=32,
@@ -428,7 +429,7 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
         ms = float(t[0])
     n_params = sum(p.numel() for p in params)
     res = {"tokens_per_s": world * micro_batch * seq / (ms * 1e-3), "ms_per_step": ms, "loss": float(loss),
-           "params": n_params, "patched": patched, "tokens_per_gpu": micro_batch * seq, "steps": steps,
+           "params": n_params, "patched": patched, "fuse_residual": bool(patched and fuse_residual), "tokens_per_gpu": micro_batch * seq, "steps": steps,
            "fused_kernel_launches_per_step": (_C.launch_count() - l0) / steps,
            "peak_mem_GB": torch.cuda.max_memory_allocated(dev) / 1e9}
     del opt, master, net, model
@@ -504,9 +505,10 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-tokens", type=int, default=8192)
-    ap.add_argument("--workload", default="opset", choices=["opset", "llama1b", "llama1b-unpatched", "vpce"],
+    ap.add_argument("--workload", default="opset", choices=["opset", "llama1b", "llama1b-fused-residual", "llama1b-unpatched", "vpce"],
                     help="opset (default): the fused operator set; llama1b: only the Llama-1B training step with "
-                         "the patch; llama1b-unpatched: the same with stock HuggingFace modules")
+                         "the patch; llama1b-fused-residual: the same with each layer's closing residual add fused "
+                         "into the next RMSNorm; llama1b-unpatched: the same with stock HuggingFace modules")
     ap.add_argument("--train-step", action="store_true",
                     help="after the operator set, also time the patched Llama-1B training step (adds ~1 min)")
     ap.add_argument("--tokens", type=int, default=0,
@@ -577,7 +579,8 @@ def main():
             dist.destroy_process_group()
         return
     if args.workload != "opset":
-        res = run_llama1b(dev, dist, world, max(1, min(args.steps, 10)), 2, patched=args.workload == "llama1b")
+        res = run_llama1b(dev, dist, world, max(1, min(args.steps, 10)), 2, patched=args.workload != "llama1b-unpatched",
+                          fuse_residual=args.workload == "llama1b-fused-residual")
         if rank == 0:
             print(json.dumps({"metric": "llama1b_train_tokens_per_s", "value": res["tokens_per_s"], "unit": "tokens/s",
                               "n_gpus": world, "steps": res["steps"], "warmup": 2, "ms_per_step": res["ms_per_step"],

@@ -8,5 +8,6 @@ from .qwen2 import trigger
 from .qwen2_vl import trigger
 from .mistral import trigger
 from .phi3 import trigger
+from ._common import residual_fusion_enabled, set_residual_fusion
 
-__all__ = ["trigger"]
+__all__ = ["trigger", "set_residual_fusion", "residual_fusion_enabled"]

@@ -9,6 +9,7 @@ values); the older tuple-returning layer protocol is kept for installs that stil
 from __future__ import annotations
 
 import inspect
+import os
 
 import torch
 import torch.nn.functional as F
@@ -19,6 +20,7 @@ from ..core.fused_add_norm import triton_fused_add_norm
 from ..core.fused_apply_rope import fused_apply_rope
 from ..core.fused_silu import triton_fused_up_gate_silu, triton_fused_up_gate_silu_no_split
 from ..core.rmsnorm import triton_rmsnorm
+from ._deferred import DeferredResidual
 
 try:  # transformers >= 4.50
     from transformers.utils import can_return_tuple
@@ -27,12 +29,35 @@ except ImportError:  # pragma: no cover
         return fn
 
 
+_fuse_residual = os.environ.get("MDY_FUSE_RESIDUAL", "0") == "1"
+
+
+def set_residual_fusion(enabled: bool) -> None:
+    """Switch the fusion of each layer's closing residual add into the next RMSNorm on or off (default off,
+    or the environment variable ``MDY_FUSE_RESIDUAL=1``).  With it on, a patched decoder layer returns a
+    :class:`DeferredResidual`; results are unchanged.  It is bypassed under gradient checkpointing and for
+    model families whose reference patch keeps add and norm separate (Mistral).  Leave it off with wrappers
+    that register hooks on layer outputs (FSDP): a hook would see the materialised sum, not the graph."""
+    global _fuse_residual
+    _fuse_residual = bool(enabled)
+
+
+def residual_fusion_enabled() -> bool:
+    return _fuse_residual
+
+
+def _eps_of(norm):
+    eps = getattr(norm, "variance_epsilon", None)
+    return norm.eps if eps is None else eps
+
+
 def rmsnorm_forward(self, hidden_state):
-    """``<Model>RMSNorm.forward`` (reference llama.py:12-13)."""
-    eps = getattr(self, "variance_epsilon", None)
-    if eps is None:
-        eps = self.eps
-    return triton_rmsnorm(hidden_state, self.weight, eps)
+    """``<Model>RMSNorm.forward`` (reference llama.py:12-13).  A deferred layer output is added and
+    normalised in one kernel."""
+    if type(hidden_state) is DeferredResidual:
+        branch, residual = hidden_state.parts()
+        return triton_fused_add_norm(branch, residual, self.weight, _eps_of(self))[0]
+    return triton_rmsnorm(hidden_state, self.weight, _eps_of(self))
 
 
 def mlp_forward(self, hidden_state):
@@ -60,11 +85,8 @@ def make_decoder_layer_forward(original_forward, fuse_add_norm: bool = True):
     def post_attention(self, attn_out, residual):
         drop = getattr(self, "resid_attn_dropout", _identity)
         ln = self.post_attention_layernorm
-        eps = getattr(ln, "variance_epsilon", None)
-        if eps is None:
-            eps = ln.eps
         if fuse_add_norm:
-            return triton_fused_add_norm(drop(attn_out), residual, ln.weight, eps)
+            return triton_fused_add_norm(drop(attn_out), residual, ln.weight, _eps_of(ln))
         residual = residual + drop(attn_out)
         return ln(residual), residual
 
@@ -72,15 +94,24 @@ def make_decoder_layer_forward(original_forward, fuse_add_norm: bool = True):
         def decoder_layer_forward(self, hidden_states, attention_mask=None, position_ids=None,
                                   past_key_values=None, use_cache=False, position_embeddings=None,
                                   **kwargs):
-            residual = hidden_states
-            hidden_states = self.input_layernorm(hidden_states)
+            if type(hidden_states) is DeferredResidual:
+                # the previous layer left its closing add to this layer's input norm (one kernel for both)
+                branch, residual = hidden_states.parts()
+                ln = self.input_layernorm
+                hidden_states, residual = triton_fused_add_norm(branch, residual, ln.weight, _eps_of(ln))
+            else:
+                residual = hidden_states
+                hidden_states = self.input_layernorm(hidden_states)
             hidden_states, _ = self.self_attn(
                 hidden_states=hidden_states, attention_mask=attention_mask, position_ids=position_ids,
                 past_key_values=past_key_values, use_cache=use_cache,
                 position_embeddings=position_embeddings, **kwargs)
             hidden_states, residual = post_attention(self, hidden_states, residual)
-            hidden_states = self.mlp(hidden_states)
-            return residual + getattr(self, "resid_mlp_dropout", _identity)(hidden_states)
+            hidden_states = getattr(self, "resid_mlp_dropout", _identity)(self.mlp(hidden_states))
+            if (_fuse_residual and fuse_add_norm
+                    and not (self.training and getattr(self, "gradient_checkpointing", False))):
+                return DeferredResidual.wrap(hidden_states, residual)
+            return residual + hidden_states
     else:  # pragma: no cover - exercised only with an old transformers install
         def decoder_layer_forward(self, hidden_states, attention_mask=None, position_ids=None,
                                   past_key_value=None, output_attentions=False, use_cache=False,

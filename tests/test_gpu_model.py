@@ -2,6 +2,7 @@
 the loss and gradients of the stock model (reference's own check: Easy-Tutorials/09-test-kernel-speed.ipynb
 cells 3-7 compare gradients before and after the patch).  The stock model runs in a child process because
 the patch is process-wide and irreversible."""
+import functools
 import json
 import subprocess
 import sys
@@ -16,9 +17,12 @@ ROOT = Path(__file__).resolve().parent.parent
 CHILD = r"""
 import json, sys, torch
 sys.path.insert(0, {root!r})
-family, patched, dtype = sys.argv[1], sys.argv[2] == "1", getattr(torch, sys.argv[3])
+family, patched, dtype = sys.argv[1], sys.argv[2] in ("1", "2"), getattr(torch, sys.argv[3])
 if patched:
     from mdy_triton.replace_kernel import *  # noqa
+    if sys.argv[2] == "2":
+        from mdy_triton.replace_kernel import set_residual_fusion
+        set_residual_fusion(True)
 import transformers
 cfg_cls, model_cls = {{"llama": (transformers.LlamaConfig, transformers.LlamaForCausalLM),
                       "qwen2": (transformers.Qwen2Config, transformers.Qwen2ForCausalLM),
@@ -40,9 +44,13 @@ model = model_cls(cfg).to("cuda").to(dtype)
 g = torch.Generator().manual_seed(1)
 ids = torch.randint(0, 2048, (3, 64), generator=g).cuda()
 labels = ids.clone(); labels[0, :10] = -100
+layer0 = [m for n, m in model.named_modules() if n.endswith("layers.0")][0]
+seen = []
+hook = layer0.register_forward_hook(lambda mod, inp, o: seen.append(type(o).__name__))
 out = model(input_ids=ids, labels=labels)
+hook.remove()
 out.loss.backward()
-res = {{"loss": float(out.loss), "logits_shape": list(out.logits.shape)}}
+res = {{"loss": float(out.loss), "logits_shape": list(out.logits.shape), "layer_output_type": seen[0]}}
 params = {{k.replace("model.language_model.", "model."): v for k, v in model.named_parameters()}}
 for name in ("model.embed_tokens.weight", "model.layers.0.input_layernorm.weight", "model.layers.1.post_attention_layernorm.weight",
              "model.layers.0.self_attn.q_proj.weight", "model.layers.0.self_attn.qkv_proj.weight", "model.layers.1.mlp.gate_proj.weight",
@@ -55,12 +63,23 @@ with torch.no_grad():
     res["eval_loss"] = float(model(input_ids=ids, labels=labels).loss)
     gen = model.generate(ids[:1, :8], max_new_tokens=4, do_sample=False)
     res["generated"] = gen[0].tolist()
+    hs = model(input_ids=ids, output_hidden_states=True).hidden_states
+    res["hidden_norms"] = [float(h.float().norm()) for h in hs]
+model.zero_grad()
+model.gradient_checkpointing_enable()
+model.train()
+out = model(input_ids=ids, labels=labels)
+out.loss.backward()
+res["ckpt_loss"] = float(out.loss)
+res["ckpt_grad"] = [float(params["lm_head.weight"].grad.float().norm()), float(params["model.embed_tokens.weight"].grad.float().norm())]
 print("RESULT " + json.dumps(res))
 """
 
 
+@functools.lru_cache(maxsize=None)
 def _run(family, patched, dtype):
-    r = subprocess.run([sys.executable, "-c", CHILD.format(root=str(ROOT)), family, "1" if patched else "0", dtype],
+    """patched: False = stock model, True = patched, 2 = patched with residual fusion switched on."""
+    r = subprocess.run([sys.executable, "-c", CHILD.format(root=str(ROOT)), family, str(int(patched)), dtype],
                        capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stderr[-3000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
@@ -75,9 +94,31 @@ def test_patched_model_matches_stock_model_fp32(family):
     assert abs(a["loss"] - b["loss"]) <= 1e-4 * max(1.0, abs(a["loss"]))
     assert abs(a["eval_loss"] - b["eval_loss"]) <= 1e-4 * max(1.0, abs(a["eval_loss"]))
     assert a["generated"] == b["generated"]
+    _same_gradients(a, b)
+    assert b["layer_output_type"] == "Tensor"
+
+
+def _same_gradients(a, b, rel=2e-3):
     for k, v in a.items():
         if isinstance(v, list) and len(v) == 2 and k not in ("logits_shape",):
-            assert abs(v[0] - b[k][0]) <= 2e-3 * max(1e-6, abs(v[0])), (k, v, b[k])
+            assert abs(v[0] - b[k][0]) <= rel * max(1e-6, abs(v[0])), (k, v, b[k])
+    assert abs(a["ckpt_loss"] - b["ckpt_loss"]) <= 1e-4 * max(1.0, abs(a["ckpt_loss"]))
+    assert len(a["hidden_norms"]) == len(b["hidden_norms"])
+    for x, y in zip(a["hidden_norms"], b["hidden_norms"]):
+        assert abs(x - y) <= 1e-3 * max(1.0, abs(x)), (a["hidden_norms"], b["hidden_norms"])
+
+
+@pytest.mark.parametrize("family", ["llama", "qwen2", "phi3", "qwen2_vl"])
+def test_residual_fusion_matches_stock_model_fp32(family):
+    """With `set_residual_fusion(True)` the layers hand a deferred sum to the next RMSNorm; loss, gradients,
+    generation, the recorded hidden states and a gradient-checkpointed step all stay those of the stock model."""
+    a = _run(family, False, "float32")
+    b = _run(family, 2, "float32")
+    assert b["layer_output_type"] == "DeferredResidual"
+    assert abs(a["loss"] - b["loss"]) <= 1e-4 * max(1.0, abs(a["loss"]))
+    assert abs(a["eval_loss"] - b["eval_loss"]) <= 1e-4 * max(1.0, abs(a["eval_loss"]))
+    assert a["generated"] == b["generated"]
+    _same_gradients(a, b)
 
 
 def test_patched_model_matches_stock_model_bf16():

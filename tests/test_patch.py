@@ -76,3 +76,31 @@ def test_patched_model_builds_on_cpu_and_refuses_to_run_there():
     ids = torch.randint(0, 128, (1, 8))
     with pytest.raises(RuntimeError, match="CUDA"):
         model(input_ids=ids, labels=ids)
+
+
+def test_deferred_residual_behaves_like_the_sum():
+    """The object a layer returns under residual fusion: every consumer other than the patched norms sees
+    branch + residual, with gradients to both parts."""
+    from mdy_triton_b200.replace_kernel._deferred import DeferredResidual
+    a = torch.randn(2, 3, 4, requires_grad=True)
+    r = torch.randn(2, 3, 4, requires_grad=True)
+    d = DeferredResidual.wrap(a * 1.0, r * 1.0)
+    assert type(d) is DeferredResidual and d.shape == (2, 3, 4) and d.dtype == torch.float32 and d.dim() == 3
+    assert d.requires_grad and d.device.type == "cpu" and d.size(-1) == 4 and d.numel() == 24
+    y = d * 2
+    assert type(y) is torch.Tensor and torch.equal(y, (a + r) * 2)
+    y.sum().backward()
+    assert torch.equal(a.grad, torch.full_like(a, 2.0)) and torch.equal(r.grad, torch.full_like(r, 2.0))
+    assert torch.equal(d[:, -1:, :], (a + r)[:, -1:, :]) and type(d[:, -1:, :]) is torch.Tensor
+    assert torch.equal(torch.stack([d, d]), torch.stack([a + r, a + r]))
+    assert torch.equal(d.float().detach(), (a + r).detach()) and torch.equal(torch.nn.functional.relu(d), torch.relu(a + r))
+    branch, residual = d.parts()
+    assert type(branch) is torch.Tensor and torch.equal(branch, a) and torch.equal(residual, r)
+
+
+def test_residual_fusion_switch():
+    from mdy_triton.replace_kernel import residual_fusion_enabled, set_residual_fusion
+    before = residual_fusion_enabled()
+    set_residual_fusion(True); assert residual_fusion_enabled()
+    set_residual_fusion(False); assert not residual_fusion_enabled()
+    set_residual_fusion(before)
