@@ -234,6 +234,15 @@ int mdy_ce_fused(const void* logits, void* dlogits, const int64_t* labels, float
  * dlogits.  buf: T [n] contiguous; scale: float device scalar. */
 int mdy_scale_inplace(void* buf, int64_t n, const float* scale, int dtype, void* stream);
 
+/* ---- row-wise max / min ------------------------------------------------------------------ */
+
+/* Replaces the launches in mdy_triton/core/triton_maxmin.py:66-97 (triton_max) and :149-179
+ * (triton_min).  x: T [M, N], inner-contiguous, row stride in elements; values: T [M]; indices: int64
+ * [M] = smallest column holding the row's maximum (take_min = 0) or minimum (take_min != 0).  A NaN in
+ * a row is returned as its extreme, as torch.max / torch.min do. */
+int mdy_rowwise_extreme(const void* x, void* values, int64_t* indices, int64_t M, int64_t N,
+                        int64_t row_stride, int take_min, int dtype, void* stream);
+
 /* Vocab-parallel combine after the all-gather of per-rank (lse_local, -x_label) planes.
  * gathered: float [tp, 2, M]; labels: int64 [M]; out lse[r] = logsumexp_t(gathered[t,0,r]);
  * losses[r] = lse[r] + sum_t gathered[t,1,r], or 0 for ignored rows.  Replaces the torch sequence at

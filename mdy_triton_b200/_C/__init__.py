@@ -47,6 +47,7 @@ SIGNATURES = {
     "mdy_get_tunable": (_I, [_I]),
     "mdy_last_device_error": (_I, [_I]),
     "mdy_ce_last_geometry": (_I, [_P, _P, _P, _P]),
+    "mdy_rowwise_extreme": (_I, [_P, _P, _P, _L, _L, _L, _I, _I, _P]),
     "mdy_rmsnorm_bwd_partial_rows": (_L, [_L, _L, _I]),
     "mdy_rmsnorm_fwd": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _F, _I, _I, _P]),
     "mdy_rmsnorm_bwd": (_I, [_P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _I, _I, _P]),

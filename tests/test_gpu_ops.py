@@ -509,6 +509,62 @@ def test_ce_cluster_launch_geometry():
     assert lib.mdy_last_device_error(1) == 0
 
 
+# --------------------------------------------------------------------------------------------- max / min
+def _first_extreme(x, take_min):
+    """Reference result on CPU in float32: the extreme of each row and the first column holding it."""
+    xf = x.float().cpu()
+    vals = xf.min(-1).values if take_min else xf.max(-1).values
+    first = (xf == vals[..., None]).float().argmax(-1)
+    return vals, first
+
+
+@pytest.mark.parametrize("shape,dt", [
+    ((64, 7), torch.float32), ((1000, 256), torch.bfloat16), ((33, 257), torch.float16), ((5, 2048), torch.bfloat16),
+    ((16, 2056), torch.float32), ((12, 128256), torch.bfloat16), ((3, 50257), torch.float32), ((1, 1), torch.float32),
+    ((2, 3, 4096), torch.bfloat16), ((300, 1001), torch.bfloat16),
+])
+@pytest.mark.parametrize("take_min", [False, True])
+def test_max_min_match_torch(shape, dt, take_min):
+    from mdy_triton.core import triton_max, triton_min
+    # few distinct values, so every row has ties: the index must be the first occurrence
+    x = torch.randint(-20, 20, shape, generator=g(sum(shape))).to(dt).to(DEV)
+    out = (triton_min if take_min else triton_max)(x)
+    vals, first = _first_extreme(x, take_min)
+    assert out.func_type == ("triton_min" if take_min else "triton_max")
+    assert out.values.dtype == dt and out.indices.dtype == torch.int64 and out.values.shape == x.shape[:-1]
+    assert torch.equal(out.values.float().cpu(), vals) and torch.equal(out.indices.cpu(), first)
+    y = torch.randn(shape, generator=g(1 + sum(shape))).to(dt).to(DEV)       # continuous values
+    v, i = (triton_min if take_min else triton_max)(y)
+    t = torch.min(y, -1) if take_min else torch.max(y, -1)
+    assert torch.equal(v, t.values) and torch.equal(y.gather(-1, i[..., None])[..., 0], t.values)
+
+
+def test_max_min_axis_keepdim_strides_and_nan():
+    from mdy_triton.core import triton_max, triton_min
+    x = torch.randn(6, 50, 40, generator=g(9)).to(DEV)
+    for axis in (0, 1, -1, -2):
+        for keepdim in (False, True):
+            a, b = triton_max(x, axis=axis, keepdim=keepdim), torch.max(x, dim=axis, keepdim=keepdim)
+            assert torch.equal(a.values, b.values) and torch.equal(a.indices, b.indices)
+            a, b = triton_min(x, axis, keepdim), torch.min(x, dim=axis, keepdim=keepdim)
+            assert torch.equal(a.values, b.values) and torch.equal(a.indices, b.indices)
+    wide = torch.randn(32, 4096 + 64, generator=g(10)).to(torch.bfloat16).to(DEV)
+    view = wide[:, 8:4096 + 8]                                   # row stride larger than the row, 16-byte aligned
+    a, b = triton_max(view), torch.max(view, -1)
+    assert torch.equal(a.values, b.values) and torch.equal(a.indices, b.indices)
+    odd = wide[:, 3:4000]                                        # misaligned rows: scalar path
+    a, b = triton_min(odd), torch.min(odd, -1)
+    assert torch.equal(a.values, b.values) and torch.equal(a.indices, b.indices)
+    n = torch.randn(4, 5000, generator=g(11)).to(DEV)
+    n[1, 77] = float("nan"); n[1, 4000] = float("nan"); n[3, 0] = float("inf")
+    for fn in (triton_max, triton_min):
+        r = fn(n)
+        assert torch.isnan(r.values[1]) and r.indices[1] == 77 and not torch.isnan(r.values[[0, 2, 3]]).any()
+    assert triton_max(n).indices[3] == 0
+    with pytest.raises(RuntimeError):
+        triton_max(torch.randn(4, 4))                            # CPU tensor: no fallback
+
+
 def test_direct_c_abi_calls_with_strides():
     """Call the entry points directly with row strides larger than the row."""
     lib = _C.lib()
