@@ -139,6 +139,16 @@ def split_no_split(x, order):
 # --------------------------------------------------------------------------------------------------
 # cross-entropy — mdy_triton/core/cross_entyopy_loss.py:13-42 (forward), :45-80 (backward), :145-149
 # --------------------------------------------------------------------------------------------------
+def rowwise_extreme(x, take_min=False):
+    """Max (or min) over the last axis with the position of its first occurrence: what the reference's
+    ``tl.max / tl.min(..., return_indices=True)`` (core/triton_maxmin.py:32, :114) and its chunked
+    update with a strict comparison (:50-63, :133-146) produce.  Values keep the input dtype."""
+    xf = _f(x)
+    vals = xf.min(-1).values if take_min else xf.max(-1).values
+    first = (xf == vals.unsqueeze(-1)).to(torch.int8).argmax(-1)
+    return vals.to(x.dtype), first
+
+
 def ce_rows(logits, labels, vocab_start=0, split=False):
     """Per-row (losses, lse) over the local slice [vocab_start, vocab_start+V) (:20-42).
     Ignored rows: 0, 0.  split=True stores -logit[label] on the owning slice, 0 elsewhere."""

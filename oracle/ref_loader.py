@@ -168,3 +168,11 @@ def ce_scalar(logits, labels, n_items=None):
         loss = m.triton_entropy_loss(lg, labels, n_items)
         loss.backward()
     return loss.detach(), lg.grad
+
+
+def extreme(x, take_min=False, axis=-1, keepdim=False):
+    """-> values, indices of reference ``triton_max`` / ``triton_min`` (core/triton_maxmin.py:66-97, :149-179)."""
+    m = load("triton_maxmin")
+    with cpu_shims():
+        r = (m.triton_min if take_min else m.triton_max)(x.detach().clone(), axis, keepdim)
+    return r.values, r.indices

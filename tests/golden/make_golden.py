@@ -1,6 +1,6 @@
 """Generate the golden vectors in this directory from the reference's own kernels.
 
-    TRITON_INTERPRET=1 python tests/golden/make_golden.py
+    TRITON_INTERPRET=1 python tests/golden/make_golden.py [file.pt ...]
 
 Needs a reference checkout (located by ``oracle/ref_loader.py``, ``MDY_REFERENCE_ROOT``).  Each case stores its
 seeded inputs and the outputs / gradients the reference operator produced for them when run on CPU
@@ -140,11 +140,33 @@ def case_ce():
     return out
 
 
+def case_maxmin():
+    out = []
+    for name, (shape, dt, seed, ties) in {
+        "short_rows_f32": ((37, 200), torch.float32, 20, False),          # reference's short-row kernel (D <= 256)
+        "short_rows_ties_bf16": ((64, 256), torch.bfloat16, 21, True),
+        # chunked long-row kernel, ragged second chunk.  Rows stay within two chunks of 2048 columns: beyond
+        # that the reference kernel skips columns (its column offsets accumulate, triton_maxmin.py:53,136)
+        "long_rows_f32": ((5, 4000), torch.float32, 22, False),
+        "long_rows_ties_f16": ((6, 4096), torch.float16, 23, True),
+        "three_dims_bf16": ((3, 4, 300), torch.bfloat16, 24, False),
+    }.items():
+        g = gen(seed)
+        x = torch.randint(-9, 9, shape, generator=g).to(dt) if ties else randn(g, *shape, dtype=dt)
+        vmax, imax = R.extreme(x, False)
+        vmin, imin = R.extreme(x, True)
+        out.append(dict(name=name, x=x, max_values=vmax, max_indices=imax, min_values=vmin, min_indices=imin))
+    return out
+
+
 def main():
     if not R.available():
         raise SystemExit(f"no reference checkout at {R.REFERENCE_ROOT}")
+    only = set(sys.argv[1:])  # optional: file names to (re)generate; default all
     for fname, fn in {"rmsnorm.pt": case_rmsnorm, "add_rmsnorm.pt": case_add_rmsnorm, "rope.pt": case_rope,
-                      "swiglu.pt": case_swiglu, "cross_entropy.pt": case_ce}.items():
+                      "swiglu.pt": case_swiglu, "cross_entropy.pt": case_ce, "maxmin.pt": case_maxmin}.items():
+        if only and fname not in only:
+            continue
         cases = fn()
         torch.save(cases, HERE / fname)
         print(fname, [c["name"] for c in cases], f"{(HERE / fname).stat().st_size / 1e6:.2f} MB")

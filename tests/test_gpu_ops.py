@@ -518,6 +518,16 @@ def _first_extreme(x, take_min):
     return vals, first
 
 
+@pytest.mark.parametrize("c", golden_cases("maxmin.pt"))
+def test_max_min_golden(c):
+    """Bit-exact against the reference kernels' stored outputs."""
+    from mdy_triton.core import triton_max, triton_min
+    x = c["x"].to(DEV)
+    for fn, key in ((triton_max, "max"), (triton_min, "min")):
+        r = fn(x)
+        assert torch.equal(r.values.cpu(), c[key + "_values"]) and torch.equal(r.indices.cpu(), c[key + "_indices"])
+
+
 @pytest.mark.parametrize("shape,dt", [
     ((64, 7), torch.float32), ((1000, 256), torch.bfloat16), ((33, 257), torch.float16), ((5, 2048), torch.bfloat16),
     ((16, 2056), torch.float32), ((12, 128256), torch.bfloat16), ((3, 50257), torch.float32), ((1, 1), torch.float32),

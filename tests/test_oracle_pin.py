@@ -107,6 +107,14 @@ def test_vocab_parallel_combine_matches_full_vocab():
     assert torch.allclose(losses, full_losses, atol=1e-5) and torch.allclose(lse, full_lse, atol=1e-5)
 
 
+@pytest.mark.parametrize("c", golden_cases("maxmin.pt"))
+def test_max_min(c):
+    """Bit-exact: values and first-occurrence indices of the reference's max / min kernels."""
+    for take_min, key in ((False, "max"), (True, "min")):
+        v, i = E.rowwise_extreme(c["x"], take_min)
+        assert torch.equal(v, c[key + "_values"]) and torch.equal(i, c[key + "_indices"])
+
+
 def test_live_reference_when_present():
     """With a reference checkout at hand, run its kernels now (Triton interpreter) instead of trusting
     only the stored vectors."""
@@ -128,3 +136,8 @@ def test_live_reference_when_present():
     ls2, lse2 = E.ce_rows(lg, lb)
     assert torch.allclose(ls, ls2, atol=1e-5)
     assert_close(dlg, E.ce_grad(lg, lb, lse2, dl), 1e-4)
+    xi = torch.randint(-5, 5, (7, 700), generator=g).float()
+    for take_min in (False, True):
+        v, i = R.extreme(xi, take_min)
+        v2, i2 = E.rowwise_extreme(xi, take_min)
+        assert torch.equal(v, v2) and torch.equal(i, i2)
