@@ -20,6 +20,8 @@ sys.path.insert(0, {root!r})
 family, patched, dtype = sys.argv[1], sys.argv[2] in ("1", "2"), getattr(torch, sys.argv[3])
 if patched:
     from mdy_triton.replace_kernel import *  # noqa
+    if family == "glm":
+        import mdy_triton.replace_kernel.glm4  # noqa  (not part of the star import, as in the reference)
     if sys.argv[2] == "2":
         from mdy_triton.replace_kernel import set_residual_fusion
         set_residual_fusion(True)
@@ -28,8 +30,11 @@ cfg_cls, model_cls = {{"llama": (transformers.LlamaConfig, transformers.LlamaFor
                       "qwen2": (transformers.Qwen2Config, transformers.Qwen2ForCausalLM),
                       "mistral": (transformers.MistralConfig, transformers.MistralForCausalLM),
                       "phi3": (transformers.Phi3Config, transformers.Phi3ForCausalLM),
+                      "glm": (transformers.GlmConfig, transformers.GlmForCausalLM),
                       "qwen2_vl": (transformers.Qwen2VLConfig, transformers.Qwen2VLForConditionalGeneration)}}[family]
-extra = {{"pad_token_id": 0}} if family == "phi3" else {{}}
+extra = {{"pad_token_id": 0}} if family in ("phi3", "glm") else {{}}
+if family == "glm":
+    extra.update(head_dim=64, partial_rotary_factor=0.5)
 text = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
             vocab_size=2048, max_position_embeddings=128, rms_norm_eps=1e-5, tie_word_embeddings=False, **extra)
 if family == "qwen2_vl":
@@ -86,7 +91,7 @@ def _run(family, patched, dtype):
     return json.loads(line[7:])
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen2", "mistral", "phi3", "qwen2_vl"])
+@pytest.mark.parametrize("family", ["llama", "qwen2", "mistral", "phi3", "qwen2_vl", "glm"])
 def test_patched_model_matches_stock_model_fp32(family):
     a = _run(family, False, "float32")
     b = _run(family, True, "float32")
@@ -108,7 +113,7 @@ def _same_gradients(a, b, rel=2e-3):
         assert abs(x - y) <= 1e-3 * max(1.0, abs(x)), (a["hidden_norms"], b["hidden_norms"])
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen2", "phi3", "qwen2_vl"])
+@pytest.mark.parametrize("family", ["llama", "qwen2", "phi3", "qwen2_vl", "glm"])
 def test_residual_fusion_matches_stock_model_fp32(family):
     """With `set_residual_fusion(True)` the layers hand a deferred sum to the next RMSNorm; loss, gradients,
     generation, the recorded hidden states and a gradient-checkpointed step all stay those of the stock model."""

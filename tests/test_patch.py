@@ -104,3 +104,16 @@ def test_residual_fusion_switch():
     set_residual_fusion(True); assert residual_fusion_enabled()
     set_residual_fusion(False); assert not residual_fusion_enabled()
     set_residual_fusion(before)
+
+
+def test_glm4_is_patched_on_explicit_import_only():
+    """The reference's package ``__init__`` does not list glm4; importing the module applies it.  RoPE
+    stays stock (reference glm4.py:5-6)."""
+    import sys
+    import transformers.models.glm.modeling_glm as m
+    if "mdy_triton_b200.replace_kernel.glm4" not in sys.modules:
+        assert m.GlmRMSNorm.forward is not _common.rmsnorm_forward
+    import mdy_triton.replace_kernel.glm4  # noqa: F401
+    _check_family("glm", "Glm", rope=False)
+    assert m.GlmMLP.forward is _common.mlp_forward_fused_proj
+    assert m.apply_rotary_pos_emb is not fused_apply_rope
