@@ -47,6 +47,10 @@ CONFIGS = {
                ffn=18944, vocab=152064, sigma=2.0, ignored=0.10, seed=2, norm="rmsnorm"),
 }
 OPS = ("norm", "rope", "swiglu", "cross_entropy")
+# (operator, direction, OpSet method): the launches of one step, in order.  The one-pass cross-entropy
+# computes loss and gradient in a single kernel.
+PHASES = (("norm", "fwd", "norm_fwd"), ("norm", "bwd", "norm_bwd"), ("rope", "fwd", "rope_fwd"), ("rope", "bwd", "rope_bwd"),
+          ("swiglu", "fwd", "swiglu_fwd"), ("swiglu", "bwd", "swiglu_bwd"), ("cross_entropy", "fwd+bwd", "cross_entropy"))
 FALLBACK_PEAK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one one-pass cross-entropy launch, from the ncu capture
 # summarised under profiles/ (None until a capture exists): bytes per row of the captured case.
@@ -175,36 +179,50 @@ class OpSet:
     def _st(self, t):  # (batch, head, position) strides of a [B, L, H, D] storage viewed as [B, H, L, D]
         return t.stride(0), t.stride(2), t.stride(1)
 
-    def norm(self):
+    def norm_fwd(self):
         C, lib, c, st = self.C, self.lib, self.cfg, self.stream
         M, H, bf = self.M, c["hidden"], C.MDY_BF16
         if c["norm"] == "add_rmsnorm":
             C.check(lib.mdy_add_rmsnorm_fwd(self.x.data_ptr(), self.res.data_ptr(), self.w.data_ptr(), self.y.data_ptr(),
                                             self.nres.data_ptr(), self.rstd.data_ptr(), M, H, H, c["eps"], bf, bf, st), "add_rmsnorm_fwd")
+        else:
+            C.check(lib.mdy_rmsnorm_fwd(self.x.data_ptr(), self.w.data_ptr(), self.y.data_ptr(), self.rstd.data_ptr(), M, H, H, H,
+                                        c["eps"], bf, bf, st), "rmsnorm_fwd")
+
+    def norm_bwd(self):
+        C, lib, c, st = self.C, self.lib, self.cfg, self.stream
+        M, H, bf = self.M, c["hidden"], C.MDY_BF16
+        if c["norm"] == "add_rmsnorm":
             C.check(lib.mdy_add_rmsnorm_bwd(self.dy.data_ptr(), self.dnres.data_ptr(), self.nres.data_ptr(), self.w.data_ptr(),
                                             self.rstd.data_ptr(), self.dx.data_ptr(), self.dw.data_ptr(), self.partial.data_ptr(),
                                             M, H, H, bf, bf, st), "add_rmsnorm_bwd")
         else:
-            C.check(lib.mdy_rmsnorm_fwd(self.x.data_ptr(), self.w.data_ptr(), self.y.data_ptr(), self.rstd.data_ptr(), M, H, H, H,
-                                        c["eps"], bf, bf, st), "rmsnorm_fwd")
             C.check(lib.mdy_rmsnorm_bwd(self.dy.data_ptr(), self.x.data_ptr(), self.w.data_ptr(), self.rstd.data_ptr(),
                                         self.dx.data_ptr(), self.dw.data_ptr(), self.partial.data_ptr(), M, H, H, H, H, bf, bf, st),
                     "rmsnorm_bwd")
 
-    def rope(self):
+    def rope_fwd(self):
         C, lib, c, st = self.C, self.lib, self.cfg, self.stream
         a = (c["B"], c["L"], c["QH"], c["KH"], c["D"], 1)
         C.check(lib.mdy_rope(self.q.data_ptr(), self.q.data_ptr(), self.k.data_ptr(), self.k.data_ptr(), self.cos.data_ptr(),
                              self.sin.data_ptr(), *a, *self._st(self.q), *self._st(self.q), *self._st(self.k), *self._st(self.k),
                              0, C.MDY_BF16, st), "rope fwd")
+
+    def rope_bwd(self):
+        C, lib, c, st = self.C, self.lib, self.cfg, self.stream
+        a = (c["B"], c["L"], c["QH"], c["KH"], c["D"], 1)
         C.check(lib.mdy_rope(self.dq.data_ptr(), self.dq_out.data_ptr(), self.dk.data_ptr(), self.dk_out.data_ptr(),
                              self.cos.data_ptr(), self.sin.data_ptr(), *a, *self._st(self.dq), *self._st(self.dq_out),
                              *self._st(self.dk), *self._st(self.dk_out), 1, C.MDY_BF16, st), "rope bwd")
 
-    def swiglu(self):
+    def swiglu_fwd(self):
         C, lib, c, st = self.C, self.lib, self.cfg, self.stream
         M, F = self.M, c["ffn"]
         C.check(lib.mdy_swiglu_fwd(self.up.data_ptr(), self.gate.data_ptr(), self.sy.data_ptr(), M, F, F, F, F, C.MDY_BF16, st), "swiglu_fwd")
+
+    def swiglu_bwd(self):
+        C, lib, c, st = self.C, self.lib, self.cfg, self.stream
+        M, F = self.M, c["ffn"]
         C.check(lib.mdy_swiglu_bwd(self.sdy.data_ptr(), self.up.data_ptr(), self.gate.data_ptr(), self.dup.data_ptr(),
                                    self.dgate.data_ptr(), M, F, F, F, F, F, F, C.MDY_BF16, st), "swiglu_bwd")
 
@@ -215,8 +233,8 @@ class OpSet:
                 "ce_fused")
 
     def step(self, events=None):
-        for i, name in enumerate(OPS):
-            getattr(self, name)()
+        for i, (_, _, method) in enumerate(PHASES):
+            getattr(self, method)()
             if events is not None:
                 events[i + 1].record()
 
@@ -233,17 +251,18 @@ def needs_l2_flush(cfg):
 
 def run_device_arm(ops: OpSet, steps, warmup, barrier, flush):
     """Times `steps` steps.  Without flushing, the step is timed as one region (events around the whole
-    loop) and the operators by events at their boundaries.  With flushing (small configs), a 256 MB
-    buffer is overwritten before every operator, outside that operator's event pair, and a step's time
-    is the sum of its operators' times."""
+    loop) and every launch group (operator x direction) by events at its boundaries.  With flushing (small
+    configs), a 256 MB buffer is overwritten before every launch group, outside its event pair, and a
+    step's time is the sum of the groups' times.  Returns total ms, ms per phase, launches."""
     scratch = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=ops.dev) if flush else None
     for _ in range(warmup):
         ops.step()
     torch.cuda.synchronize()
     barrier()
     l0 = ops.C.launch_count()
+    n = len(PHASES)
     if not flush:
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(len(OPS) + 1)] for _ in range(steps)]
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n + 1)] for _ in range(steps)]
         t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
         t0.record()
         for s in range(steps):
@@ -253,20 +272,51 @@ def run_device_arm(ops: OpSet, steps, warmup, barrier, flush):
         torch.cuda.synchronize()
         barrier()
         total_ms = t0.elapsed_time(t1)
-        per_op_ms = {name: statistics.mean(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(steps)) for i, name in enumerate(OPS)}
+        phase_ms = [statistics.mean(ev[s][i].elapsed_time(ev[s][i + 1]) for s in range(steps)) for i in range(n)]
     else:
-        ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in OPS] for _ in range(steps)]
+        ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in PHASES] for _ in range(steps)]
         for s in range(steps):
-            for i, name in enumerate(OPS):
+            for i, (_, _, method) in enumerate(PHASES):
                 scratch.fill_(s & 0xff)
                 ev[s][i][0].record()
-                getattr(ops, name)()
+                getattr(ops, method)()
                 ev[s][i][1].record()
         torch.cuda.synchronize()
         barrier()
-        per_op_ms = {name: statistics.mean(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(steps)) for i, name in enumerate(OPS)}
-        total_ms = sum(per_op_ms.values()) * steps
-    return total_ms, per_op_ms, ops.C.launch_count() - l0
+        phase_ms = [statistics.mean(ev[s][i][0].elapsed_time(ev[s][i][1]) for s in range(steps)) for i in range(n)]
+        total_ms = sum(phase_ms) * steps
+    return total_ms, phase_ms, ops.C.launch_count() - l0
+
+
+def run_graph_replay(ops: OpSet, launches=32, replays=5):
+    """Launch-free kernel time of the small configs: each launch group captured `launches` times back to
+    back into a CUDA graph and replayed; microseconds per launch group.  The inputs of these configs fit
+    the L2, so this is not an HBM figure: it shows what is left when launch latency is taken away."""
+    out = []
+    side = torch.cuda.Stream(ops.dev)
+    saved = ops.stream
+    for _, _, method in PHASES:
+        graph = torch.cuda.CUDAGraph()
+        side.wait_stream(torch.cuda.current_stream(ops.dev))
+        with torch.cuda.stream(side):
+            ops.stream = side.cuda_stream
+            getattr(ops, method)()  # first call outside the capture
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                ops.stream = torch.cuda.current_stream(ops.dev).cuda_stream
+                for _ in range(launches):
+                    getattr(ops, method)()
+        ops.stream = saved
+        torch.cuda.synchronize()
+        graph.replay()
+        t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(replays):
+            graph.replay()
+        t1.record()
+        torch.cuda.synchronize()
+        out.append(t0.elapsed_time(t1) * 1e3 / (replays * launches))
+    return out
 
 
 # --------------------------------------------------------------------------------------------- e2e arm
@@ -599,13 +649,20 @@ def main():
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-    total_ms, per_op_ms, launches = run_device_arm(ops, args.steps, warmup, barrier, flush)
+    total_ms, phase_ms, launches = run_device_arm(ops, args.steps, warmup, barrier, flush)
+    per_op_ms = {n: sum(ms for (op, _, _), ms in zip(PHASES, phase_ms) if op == n) for n in OPS}
     total_ms = max_over_ranks(total_ms)
     ms_per_step = total_ms / args.steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
     peak, peak_src = measured_peak()
     per_op = {n: {"ms": per_op_ms[n], "GB/s": ab[n] / (per_op_ms[n] * 1e-3) / 1e9,
                   "frac_of_peak": ab[n] / (per_op_ms[n] * 1e-3) / 1e9 / peak, "algorithmic_bytes": ab[n]} for n in OPS}
+    for (op, direction, _), ms in zip(PHASES, phase_ms):
+        if direction in ("fwd", "bwd"):
+            per_op[op][direction + "_ms"] = ms
+    if flush and rank == 0:
+        for (op, direction, _), us in zip(PHASES, run_graph_replay(ops)):
+            per_op[op].setdefault("graph_replay_us", {})[direction] = us
 
     e2e = None
     if not args.no_e2e:

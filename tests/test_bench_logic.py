@@ -41,3 +41,15 @@ def test_reference_arm_prints_the_contract_line():
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["value"] == d["value"]
     assert d["metric"] == "fused_opset_fwd_bwd_algorithmic_hbm_throughput"
+
+
+def test_phases_cover_every_operator_once_per_direction():
+    """A step is seven launch groups: forward and backward of three operators plus the one-pass loss; each
+    names an OpSet method, and every operator of the byte table is covered."""
+    ops = [op for op, _, _ in bench.PHASES]
+    assert set(ops) == set(bench.OPS) and ops == sorted(ops, key=bench.OPS.index)
+    for op in ("norm", "rope", "swiglu"):
+        assert [d for o, d, _ in bench.PHASES if o == op] == ["fwd", "bwd"]
+    assert [d for o, d, _ in bench.PHASES if o == "cross_entropy"] == ["fwd+bwd"]
+    for _, _, method in bench.PHASES:
+        assert callable(getattr(bench.OpSet, method))
