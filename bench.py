@@ -54,7 +54,7 @@ PHASES = (("norm", "fwd", "norm_fwd"), ("norm", "bwd", "norm_bwd"), ("rope", "fw
 FALLBACK_PEAK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one one-pass cross-entropy launch, from the ncu capture
 # summarised under profiles/ (None until a capture exists): bytes per row of the captured case.
-CE_TRAFFIC_BYTES_PER_ROW = 499036  # (1.0508 GB + 0.9933 GB) / 4096 rows at V = 128256, bf16
+CE_TRAFFIC_BYTES_PER_ROW = 499181
 
 
 def algorithmic_bytes(cfg, tokens, ignored_frac, s=2):
@@ -418,7 +418,36 @@ def run_cpu_baseline(cfg, tokens, steps, warmup, seed):
 
 
 # ------------------------------------------------------------------------------------ Llama-1B train step
-def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, seq=4096, fuse_residual=False):
+def fused_share_of_gpu_time(step_fn, steps=2):
+    """After the timed region: run `steps` more steps under torch's kernel profiler and return the part of
+    the summed GPU kernel time spent in this library's kernels (their names carry the `mdy::` namespace).
+    A share taken under a profiler, reported beside the tokens/s, never used for it."""
+    try:
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(steps):
+                step_fn()
+            torch.cuda.synchronize()
+        total = ours = 0.0
+        by_kernel = {}
+        for e in prof.key_averages():
+            t = float(getattr(e, "device_time_total", 0.0) or getattr(e, "cuda_time_total", 0.0))
+            if t <= 0:
+                continue
+            total += t
+            if "mdy::" in e.key:
+                ours += t
+                short = e.key.split("mdy::")[-1].replace("(anonymous namespace)::", "").split("<")[0].split("(")[0]
+                by_kernel[short] = by_kernel.get(short, 0.0) + t
+        if total <= 0:
+            return None
+        return {"share": ours / total, "by_kernel": {k: v / total for k, v in sorted(by_kernel.items(), key=lambda kv: -kv[1])}}
+    except Exception as e:  # noqa: BLE001 - profiling support is optional on the box
+        return {"error": f"{type(e).__name__}: {e}"[:200]}
+
+
+def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, seq=4096, fuse_residual=False,
+                ddp_bucket_mb=25, profile_share=False):
     """Training-step workload: random-init Llama-style 1B decoder (16 layers, hidden 2048, 32 q / 8 kv heads,
     head_dim 64, FFN 8192, vocab 128256, eps 1e-5, theta 5e5), bf16 parameters with float32 master weights
     and AdamW state, full forward+backward+optimizer step, synthetic tokens uniform in the vocabulary,
@@ -439,23 +468,28 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
     model.config.use_cache = False
     net = model
     if dist is not None:
-        net = nn.parallel.DistributedDataParallel(model, device_ids=[dev.index], gradient_as_bucket_view=True)
+        net = nn.parallel.DistributedDataParallel(model, device_ids=[dev.index], gradient_as_bucket_view=True,
+                                                  bucket_cap_mb=ddp_bucket_mb)
     params = [p for p in model.parameters() if p.requires_grad]
     master = [p.detach().float().clone() for p in params]          # float32 master weights
     opt = torch.optim.AdamW(master, lr=1e-4, weight_decay=0.01, fused=True)
     g = torch.Generator(dev).manual_seed(7 + (dist.get_rank() if dist is not None else 0))
     ids = torch.randint(0, cfg.vocab_size, (micro_batch, seq), device=dev, generator=g)
 
+    for m_ in master:
+        m_.grad = torch.empty_like(m_)                               # float32 gradients, overwritten every step
+    master_grads = [m_.grad for m_ in master]
+
     def step():
         out = net(input_ids=ids, labels=ids)
         out.loss.backward()
-        for m_, p_ in zip(master, params):
-            m_.grad = p_.grad.float()
+        with torch.no_grad():
+            torch._foreach_copy_(master_grads, [p_.grad for p_ in params])   # float32 <- bf16, one multi-tensor launch
+        for p_ in params:
             p_.grad = None
         opt.step()
         with torch.no_grad():
             torch._foreach_copy_(params, master)                     # bf16 <- float32 master
-        opt.zero_grad(set_to_none=True)
         return out.loss.detach()
 
     for _ in range(warmup):
@@ -477,12 +511,19 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t[0])
+    share = None
+    if profile_share and (dist is None or dist.get_rank() == 0):
+        share = fused_share_of_gpu_time(step)
+    if dist is not None:
+        dist.barrier()
     n_params = sum(p.numel() for p in params)
     res = {"tokens_per_s": world * micro_batch * seq / (ms * 1e-3), "ms_per_step": ms, "loss": float(loss),
-           "params": n_params, "patched": patched, "fuse_residual": bool(patched and fuse_residual), "tokens_per_gpu": micro_batch * seq, "steps": steps,
+           "params": n_params, "patched": patched, "ddp_bucket_mb": ddp_bucket_mb, "fuse_residual": bool(patched and fuse_residual), "tokens_per_gpu": micro_batch * seq, "steps": steps,
            "fused_kernel_launches_per_step": (_C.launch_count() - l0) / steps,
            "peak_mem_GB": torch.cuda.max_memory_allocated(dev) / 1e9}
-    del opt, master, net, model
+    if share is not None:
+        res["fused_ops_share_of_gpu_kernel_time"] = share
+    del opt, master, master_grads, net, model
     torch.cuda.empty_cache()
     return res
 
@@ -559,6 +600,9 @@ def main():
                     help="opset (default): the fused operator set; llama1b: only the Llama-1B training step with "
                          "the patch; llama1b-fused-residual: the same with each layer's closing residual add fused "
                          "into the next RMSNorm; llama1b-unpatched: the same with stock HuggingFace modules")
+    ap.add_argument("--profile-share", action="store_true",
+                    help="llama1b workloads: after timing, profile two more steps and report the share of GPU kernel time spent in the fused kernels")
+    ap.add_argument("--ddp-bucket-mb", type=int, default=25, help="DDP gradient bucket size for the llama1b workloads")
     ap.add_argument("--train-step", action="store_true",
                     help="after the operator set, also time the patched Llama-1B training step (adds ~1 min)")
     ap.add_argument("--tokens", type=int, default=0,
@@ -630,7 +674,7 @@ def main():
         return
     if args.workload != "opset":
         res = run_llama1b(dev, dist, world, max(1, min(args.steps, 10)), 2, patched=args.workload != "llama1b-unpatched",
-                          fuse_residual=args.workload == "llama1b-fused-residual")
+                          fuse_residual=args.workload == "llama1b-fused-residual", ddp_bucket_mb=args.ddp_bucket_mb, profile_share=args.profile_share)
         if rank == 0:
             print(json.dumps({"metric": "llama1b_train_tokens_per_s", "value": res["tokens_per_s"], "unit": "tokens/s",
                               "n_gpus": world, "steps": res["steps"], "warmup": 2, "ms_per_step": res["ms_per_step"],
