@@ -71,6 +71,12 @@ def test_argument_rejection_needs_no_device():
     assert lib.mdy_ce_fused(one, None, one, one, one, None, 1.0, 4, 16, 16, 0, None) == -1
     assert lib.mdy_ce_vp_combine(one, one, one, one, 0, 4, None) == -3
     assert lib.mdy_scale_inplace(None, 4, None, 0, None) == -1
+    assert lib.mdy_rowwise_extreme(None, one, one, 4, 8, 8, 0, 0, None) == -1
+    assert lib.mdy_rowwise_extreme(one, one, one, 4, 0, 8, 0, 0, None) == -3                      # empty rows
+    assert lib.mdy_rowwise_extreme(one, one, one, 4, 8, 4, 1, 0, None) == -3                      # stride < N
+    assert lib.mdy_rowwise_extreme(one, one, one, 4, 8, 8, 0, 5, None) == -2
+    assert lib.mdy_rowwise_extreme(None, None, None, 0, 8, 8, 0, 0, None) == 0
+    assert lib.mdy_ce_last_geometry(None, None, None, None) == -5                                 # nothing launched yet
     # zero-sized problems are accepted and do nothing
     assert lib.mdy_swiglu_fwd(None, None, None, 0, 8, 8, 8, 8, 0, None) == 0
     assert lib.mdy_ce_fwd(None, None, None, None, 0, 16, 16, 0, 0, 0, None) == 0
@@ -94,6 +100,10 @@ def test_operators_refuse_cpu_tensors():
         core.fast_cross_entropy_loss(torch.randn(2, 3, 10), torch.zeros(2, 3, dtype=torch.long))
     with pytest.raises(RuntimeError, match="CUDA"):
         core.triton_entropy_loss(torch.randn(6, 10, requires_grad=True), torch.zeros(6, dtype=torch.long))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        core.triton_max(x)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        core.triton_min(x, axis=0, keepdim=True)
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):
