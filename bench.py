@@ -437,7 +437,8 @@ def fused_share_of_gpu_time(step_fn, steps=2):
             total += t
             if "mdy::" in e.key:
                 ours += t
-                short = e.key.split("mdy::")[-1].replace("(anonymous namespace)::", "").split("<")[0].split("(")[0]
+                short = e.key.split("mdy::", 1)[1].replace("(anonymous namespace)::", "").replace("<unnamed>::", "")
+                short = short.split("<")[0].split("(")[0]
                 by_kernel[short] = by_kernel.get(short, 0.0) + t
         if total <= 0:
             return None
@@ -511,6 +512,7 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
         t = torch.tensor([ms], dtype=torch.float64, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t[0])
+    fused_launches = (_C.launch_count() - l0) / steps
     share = None
     if profile_share and (dist is None or dist.get_rank() == 0):
         share = fused_share_of_gpu_time(step)
@@ -519,7 +521,7 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
     n_params = sum(p.numel() for p in params)
     res = {"tokens_per_s": world * micro_batch * seq / (ms * 1e-3), "ms_per_step": ms, "loss": float(loss),
            "params": n_params, "patched": patched, "ddp_bucket_mb": ddp_bucket_mb, "fuse_residual": bool(patched and fuse_residual), "tokens_per_gpu": micro_batch * seq, "steps": steps,
-           "fused_kernel_launches_per_step": (_C.launch_count() - l0) / steps,
+           "fused_kernel_launches_per_step": fused_launches,
            "peak_mem_GB": torch.cuda.max_memory_allocated(dev) / 1e9}
     if share is not None:
         res["fused_ops_share_of_gpu_kernel_time"] = share
