@@ -54,7 +54,7 @@ PHASES = (("norm", "fwd", "norm_fwd"), ("norm", "bwd", "norm_bwd"), ("rope", "fw
 FALLBACK_PEAK_GBS = 6650.0
 # dram__bytes_read.sum + dram__bytes_write.sum of one one-pass cross-entropy launch, from the ncu capture
 # summarised under profiles/ (None until a capture exists): bytes per row of the captured case.
-CE_TRAFFIC_BYTES_PER_ROW = 499181
+CE_TRAFFIC_BYTES_PER_ROW = 499109
 
 
 def algorithmic_bytes(cfg, tokens, ignored_frac, s=2):
