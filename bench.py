@@ -624,7 +624,7 @@ def main():
                 f"{cfg['QH']}q/{cfg['KH']}kv x {cfg['D']}; SwiGLU {cfg['ffn']}; cross-entropy vocab {cfg['vocab']}")
     flush = needs_l2_flush(cfg)
     config = {"workload": workload, "tokens_per_gpu": cfg["B"] * cfg["L"], "sharding": "tokens, one shard per GPU, no collective",
-              "l2": ("a 256 MB buffer is overwritten before every operator (outside its timed region): the tensors fit L2"
+              "l2": ("L2 flushed: a 256 MB buffer is overwritten before every launch group (outside its timed region), the tensors fit L2"
                      if flush else "every tensor streamed per step is larger than the 126 MB L2 (no flush needed)")}
     metric, unit = "fused_opset_fwd_bwd_algorithmic_hbm_throughput", "GB/s"
 
