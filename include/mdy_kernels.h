@@ -56,7 +56,7 @@ int64_t mdy_launch_count(void);
 const char* mdy_status_string(int status);
 /* Integer tunables (grid/block shape knobs used for on-device tuning).  Unknown id -> MDY_ERR_ARG.
  * value <= 0 restores the built-in default. */
-#define MDY_TUNE_CE_THREADS 0        /* threads per CTA of the row-per-CTA cross-entropy kernels   */
+#define MDY_TUNE_CE_THREADS 0        /* threads per CTA of the row-per-CTA cross-entropy kernels (default: by row length) */
 #define MDY_TUNE_CE_FUSED_CTAS_PER_SM 1 /* resident CTAs per SM the L2-resident fused CE grid assumes */
 #define MDY_TUNE_NORM_CTAS_PER_SM 2  /* persistent-grid width of the norm kernels, in CTAs per SM  */
 #define MDY_TUNE_SWIGLU_UNROLL 3     /* 16-byte vectors per thread in SwiGLU (1, 2 or 4)           */

@@ -277,6 +277,22 @@ inline int ce_threads() {
   return t;
 }
 
+// CTA sizes of the two-phase kernels when the tunable leaves the choice open (measured at 16384 rows,
+// bf16, V from 2000 to 256000).  The statistics sweep runs best with many small CTAs per SM whatever the
+// row length (V = 128256: 6380 GB/s with 128 threads, 5290 with 512; V = 4000: 3300 against 790); the
+// gradient sweep wants small CTAs only for short rows (V = 4000: 5540 against 2110 GB/s) and 512
+// threads for long ones.
+inline int ce_fwd_threads(int64_t row_bytes) {
+  const int t = tunable(MDY_TUNE_CE_THREADS);
+  if (t >= 64 && t <= 1024 && !(t & 31)) return t;
+  return row_bytes <= 32 * 1024 ? 64 : 128;
+}
+inline int ce_bwd_threads(int64_t row_bytes) {
+  const int t = tunable(MDY_TUNE_CE_THREADS);
+  if (t >= 64 && t <= 1024 && !(t & 31)) return t;
+  return row_bytes <= 16 * 1024 ? 64 : row_bytes <= 32 * 1024 ? 128 : row_bytes <= 64 * 1024 ? 256 : 512;
+}
+
 template <typename T>
 inline bool rows_vec_ok(const void* a, const void* b, int64_t rs) {
   constexpr int VE = VecInfo<T>::kElems;
@@ -305,7 +321,7 @@ int mdy_ce_fwd(const void* logits, const int64_t* labels, float* losses, float* 
   if (!logits || !labels || !losses || !lse) return MDY_ERR_NULL;
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
-    ce_fwd_kernel<T><<<(unsigned)M, ce_threads(), 0, (cudaStream_t)stream>>>(
+    ce_fwd_kernel<T><<<(unsigned)M, ce_fwd_threads(V * (int64_t)sizeof(T)), 0, (cudaStream_t)stream>>>(
         (const T*)logits, labels, losses, lse, V, row_stride, vocab_start, split,
         rows_vec_ok<T>(logits, nullptr, row_stride));
     return finish_launch(1);
@@ -322,7 +338,7 @@ int mdy_ce_bwd(const void* dlosses, int64_t dloss_stride, int dloss_dtype, const
   if (!dlosses || !logits || !dlogits || !labels || !lse) return MDY_ERR_NULL;
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
-    ce_bwd_kernel<T><<<(unsigned)M, ce_threads(), 0, (cudaStream_t)stream>>>(
+    ce_bwd_kernel<T><<<(unsigned)M, ce_bwd_threads(V * (int64_t)sizeof(T)), 0, (cudaStream_t)stream>>>(
         dlosses, dloss_stride, dloss_dtype, (const T*)logits, (T*)dlogits, labels, lse, V, row_stride,
         vocab_start, fill_ignored, rows_vec_ok<T>(logits, dlogits, row_stride));
     return finish_launch(1);
