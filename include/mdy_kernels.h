@@ -54,29 +54,9 @@ int mdy_num_sms(void);
 int64_t mdy_launch_count(void);
 /* Human-readable text for a return code of this ABI (static storage). */
 const char* mdy_status_string(int status);
-/* Integer tunables (grid/block shape knobs used for on-device tuning).  Unknown id -> MDY_ERR_ARG.
- * value <= 0 restores the built-in default. */
-#define MDY_TUNE_CE_THREADS 0        /* threads per CTA of the row-per-CTA cross-entropy kernels (default: by row length) */
-#define MDY_TUNE_CE_FUSED_CTAS_PER_SM 1 /* resident CTAs per SM the L2-resident fused CE grid assumes */
-#define MDY_TUNE_NORM_CTAS_PER_SM 2  /* persistent-grid width of the norm kernels, in CTAs per SM  */
-#define MDY_TUNE_SWIGLU_UNROLL 3     /* 16-byte vectors per thread in SwiGLU (1, 2 or 4)           */
-#define MDY_TUNE_CE_FUSED_IMPL 4     /* 0 auto, 1 row-per-CTA kernel, 2 cluster kernel staging the row in shared
-                                        memory, 3 cluster kernel keeping the row's exponentials in registers,
-                                        4 cluster kernel caching the exponentials in shared memory */
-#define MDY_TUNE_ROPE_THREADS 5      /* threads per CTA of the RoPE kernel                         */
-#define MDY_TUNE_CE_CLUSTER_SLICE_KB 6 /* largest slice of a row one CTA of the cluster kernel stages (KiB) */
-#define MDY_TUNE_CE_CLUSTER_THREADS 7  /* threads per CTA of the cluster kernel; with ids 8 and 15 selects a compiled shape:
-                                          (threads, vectors, CTAs/SM) = (256,4,3) (256,8,2) (512,2,2) (512,4,1) (1024,2,1) */
-#define MDY_TUNE_CE_CLUSTER_VPC 8      /* 16-byte vectors per thread per chunk there */
-#define MDY_TUNE_CE_REG_SHAPE 9        /* impl 3: 0/3 = 512 threads x 8 vectors, 1 = 256x8, 2 = 512x4, 4 = 1024x4;
-                                          impl 4 / auto: 0 = smallest CTA that fits, 1 = 512, 2 = 1024 threads */
-#define MDY_TUNE_ROPE_HEADS_PER_THREAD 10 /* heads a RoPE thread rotates per work item: 1, 2 or 4       */
-#define MDY_TUNE_ROPE_GRID_PER_SM 11      /* cap of the RoPE grid, in CTAs per SM (grid-stride loop)       */
-#define MDY_TUNE_NORM_BWD_THREADS 12      /* smallest CTA of the norm backward kernels: 128, 256 or 512    */
-#define MDY_TUNE_NORM_FWD_VPT 13          /* 16-byte vectors per thread the norm forward plans for: 1, 2, 4 */
-#define MDY_TUNE_NORM_BWD_VPT 14          /* the same for the norm backward                                 */
-#define MDY_TUNE_CE_CLUSTER_MINB 15        /* CTAs per SM that shape is compiled for (register cap)                 */
-#define MDY_TUNE_COUNT 16
+/* Integer knobs for on-device tuning and tests (grid and CTA shapes, kernel selection).  They are not part
+ * of the stable interface: the ids are listed in the library's own csrc/tunables.h and mirrored by the
+ * Python loader.  Unknown id -> MDY_ERR_ARG; value <= 0 restores the built-in default. */
 int mdy_set_tunable(int id, int value);
 /* Kernels that wait on hardware barriers bound every wait; if one ever expires they record a non-zero
  * code in a device flag and run to completion with a wrong result instead of hanging.  This call
@@ -120,11 +100,14 @@ int mdy_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
  * a region where cudaMalloc (and torch's caching allocator, which may fall through to it) must not run.
  * It has no counterpart in the reference, which always allocates the partials with torch
  * (core/rmsnorm.py:80).  The partial rows live in a fixed 16 MiB array inside the library's device image
- * (held by every GPU that loads the library until the process exits), so nothing is allocated or freed,
- * here or in any routine this calls.
- *   limit      mdy_rmsnorm_bwd_partial_rows(M, N, dtype) * N <= 4 * 2^20 floats (on a 148-SM B200:
- *              N <= 14168 with 16-bit activations); larger problems return MDY_ERR_UNSUPPORTED and
- *              launch nothing.
+ * (held by every GPU that loads the library until the process exits: the driver sets the array's memory
+ * aside when it loads the library's device image on a GPU, which with lazy loading is the first call of
+ * any RMSNorm entry point there, not a later call of this one), so this entry point allocates and frees
+ * nothing, here or in any routine it calls.
+ *   limit      partial rows of this launch * N <= 4 * 2^20 floats, with the partial rows worked out once
+ *              per call and that same number both checked and launched (at most
+ *              mdy_rmsnorm_bwd_partial_rows(M, N, dtype); on a 148-SM B200: N <= 14168 with 16-bit
+ *              activations); larger problems return MDY_ERR_UNSUPPORTED and launch nothing.
  *   first call on each device resolves the array's device address (cudaGetSymbolAddress) with that
  *              device current; make that first call outside any stream capture.
  *   sharing    every call on a device uses the same array.  Nothing in it has to start at zero (each

@@ -27,13 +27,17 @@ TUNE_ROPE_THREADS = 5
 TUNE_CE_CLUSTER_SLICE_KB = 6
 TUNE_CE_CLUSTER_THREADS = 7
 TUNE_CE_CLUSTER_VPC = 8
-TUNE_CE_REG_SHAPE = 9
+TUNE_CE_WAIT_TEST = 9
 TUNE_ROPE_HEADS_PER_THREAD = 10
 TUNE_ROPE_GRID_PER_SM = 11
 TUNE_NORM_BWD_THREADS = 12
 TUNE_NORM_FWD_VPT = 13
 TUNE_NORM_BWD_VPT = 14
 TUNE_CE_CLUSTER_MINB = 15
+TUNE_NORM_POW2_GROUPS = 16
+TUNE_NORM_FWD_GROUP = 17
+TUNE_NORM_BWD_GROUP = 18
+TUNE_NORM_FWD_THREADS = 19
 
 _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 

@@ -40,7 +40,7 @@ def sources() -> list[Path]:
 
 
 def _deps() -> list[Path]:
-    return sources() + sorted(CSRC.glob("*.cuh")) + sorted(INCLUDE.glob("*.h")) + [Path(__file__)]
+    return sources() + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + sorted(INCLUDE.glob("*.h")) + [Path(__file__)]
 
 
 def is_stale() -> bool:

@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 #include "../../include/mdy_kernels.h"
+#include "tunables.h"
 
 namespace mdy {
 

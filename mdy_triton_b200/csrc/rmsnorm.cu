@@ -1,7 +1,8 @@
 // RMSNorm and fused add+RMSNorm, forward and backward, for sm_100a.
 //
 // Layout: activations are [M, N] row-major with a row stride.  A row is owned by a GROUP of G
-// threads (G = 32..1024, a power of two); each thread keeps VPT 16-byte vectors of the row in
+// threads (G = 32..1024, a multiple of 32 chosen so that G * VPT covers the row with as few idle
+// lanes as possible: 448 vectors -> 224 x 2); each thread keeps VPT 16-byte vectors of the row in
 // registers, so the row is read from HBM exactly once in forward (sum of squares and scaling use
 // the same registers) and x/dy exactly once in backward.  A CTA holds blockDim/G groups and walks a
 // persistent row loop; the weight vector stays in registers across the loop.  The in-group reduction
@@ -21,19 +22,32 @@ struct RowPlan {
   int gpc;   // rows (groups) per CTA
 };
 
-inline RowPlan plan_rows(int64_t nvec, int min_bt, int pref_vpt = 2) {
+// `group` > 0 forces the threads per row (rounded up to a warp multiple); 0 = choose.
+inline RowPlan plan_rows(int64_t nvec, int min_bt, int pref_vpt, int group) {
   RowPlan p{0, 0, 0, 0};
   if (nvec <= 0 || nvec > 8192) return p;
-  // two vectors per thread; G a power of two (a group of 224 threads for 448 vectors measured slower than
-  // 256 threads with idle lanes)
   if (pref_vpt != 1 && pref_vpt != 4) pref_vpt = 2;
-  int64_t G = next_pow2(ceil_div(nvec, pref_vpt));
+  int64_t G;
+  if (group > 0) {
+    G = ceil_div(group, 32) * 32;
+  } else if (tunable(MDY_TUNE_NORM_POW2_GROUPS) > 0) {
+    G = next_pow2(ceil_div(nvec, pref_vpt));
+  } else {
+    // smallest warp multiple that covers the row with pref_vpt vectors per thread
+    G = ceil_div(ceil_div(nvec, pref_vpt), 32) * 32;
+  }
   if (G < 32) G = 32;
   if (G > 1024) G = 1024;
   int64_t need = ceil_div(nvec, G);
   p.vpt = need <= 1 ? 1 : need <= 2 ? 2 : need <= 4 ? 4 : 8;
   p.G = (int)G;
-  p.gpc = G >= min_bt ? 1 : (int)(min_bt / G);
+  // as many rows per CTA as fit the CTA size asked for (at least one, never more than 1024 threads)
+  if (G < 1024 && need > 4) return plan_rows(nvec, min_bt, pref_vpt, 0);  // a forced group too small for the row
+  // as many rows per CTA as come closest to the CTA size asked for; CTAs of more than 512 threads only
+  // where one row needs them (they are limited to 64 registers per thread)
+  p.gpc = G >= min_bt ? 1 : (int)((min_bt + G / 2) / G);
+  if (p.gpc < 1) p.gpc = 1;
+  while (p.gpc > 1 && p.G * p.gpc > 512) --p.gpc;
   p.BT = p.G * p.gpc;
   return p;
 }
@@ -63,12 +77,32 @@ __device__ __forceinline__ float load_w(const void* w, int64_t idx, int w_dtype)
   return __bfloat162float(__ldg((const __nv_bfloat16*)w + idx));
 }
 
+// The VE weights of 16-byte activation vector `v` as floats.  `wvec`: the weight base is 16-byte
+// aligned, so they come in one or two vector loads instead of VE scalar ones (the weight load is the
+// head of every CTA's dependency chain, which is what short launches are made of).
+template <int VE>
+__device__ __forceinline__ void load_w_vec(const void* w, int v, int w_dtype, bool wvec, float* out) {
+  if (wvec && w_dtype == MDY_F32) {
+#pragma unroll
+    for (int h = 0; h < VE / 4; ++h) {
+      const uint4 q = ld_reuse((const float*)w + (int64_t)v * VE + h * 4);
+      unpack<float>(q, out + h * 4);
+    }
+  } else if (wvec && VE == 8) {
+    const uint4 q = ld_reuse((const uint16_t*)w + (int64_t)v * VE);
+    if (w_dtype == MDY_F16) unpack<__half>(q, out); else unpack<__nv_bfloat16>(q, out);
+  } else {
+#pragma unroll
+    for (int e = 0; e < VE; ++e) out[e] = load_w(w, (int64_t)v * VE + e, w_dtype);
+  }
+}
+
 template <typename T, int VPT, bool ADD, int MAXT>
 __global__ void __launch_bounds__(MAXT)
 norm_fwd_vec(const T* __restrict__ x, const T* __restrict__ res, const void* __restrict__ w,
              int w_dtype, T* __restrict__ y, T* __restrict__ new_res, float* __restrict__ rstd_out,
              int64_t M, int N, int64_t x_rs, int64_t res_rs, int64_t y_rs, int64_t nres_rs,
-             float eps, int G) {
+             float eps, int G, bool wvec) {
   constexpr int VE = VecInfo<T>::kElems;
   extern __shared__ float smem[];
   const int nvec = N / VE;
@@ -83,8 +117,12 @@ norm_fwd_vec(const T* __restrict__ x, const T* __restrict__ res, const void* __r
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = t + i * G;
+    if (v < nvec) {
+      load_w_vec<VE>(w, v, w_dtype, wvec, wf[i]);
+    } else {
 #pragma unroll
-    for (int e = 0; e < VE; ++e) wf[i][e] = v < nvec ? load_w(w, (int64_t)v * VE + e, w_dtype) : 0.f;
+      for (int e = 0; e < VE; ++e) wf[i][e] = 0.f;
+    }
   }
 
   // Software pipeline (CTAs of up to 512 threads): the next row's loads are issued before the current
@@ -193,7 +231,7 @@ __global__ void __launch_bounds__(MAXT)
 norm_bwd_vec(const T* __restrict__ dy, const T* __restrict__ x, const void* __restrict__ w,
              int w_dtype, const float* __restrict__ rstd_in, const T* __restrict__ dres, T* __restrict__ dx,
              float* __restrict__ dw_partial, int64_t M, int N, int64_t dy_rs, int64_t x_rs,
-             int64_t dres_rs, int64_t dx_rs, int G) {
+             int64_t dres_rs, int64_t dx_rs, int G, bool wvec) {
   constexpr int VE = VecInfo<T>::kElems;
   extern __shared__ float smem[];
   const int nvec = N / VE;
@@ -210,9 +248,10 @@ norm_bwd_vec(const T* __restrict__ dy, const T* __restrict__ x, const void* __re
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
     const int v = t + i * G;
+    if (v < nvec) load_w_vec<VE>(w, v, w_dtype, wvec, wf[i]);
 #pragma unroll
     for (int e = 0; e < VE; ++e) {
-      wf[i][e] = v < nvec ? load_w(w, (int64_t)v * VE + e, w_dtype) : 0.f;
+      if (v >= nvec) wf[i][e] = 0.f;
       acc[i][e] = 0.f;
     }
   }
@@ -394,10 +433,14 @@ inline int bwd_per_sm(const RowPlan& p) {
   return p.BT >= 512 ? 1 : 2;
 }
 
-// smallest CTA of the backward kernels (a row group of G threads may need more)
+// CTA size the backward kernels aim for (a row group of more threads gets a CTA of its own)
 inline int bwd_min_threads() {
   const int t = tunable(MDY_TUNE_NORM_BWD_THREADS);
   return (t == 128 || t == 256 || t == 512) ? t : 512;
+}
+inline int fwd_min_threads() {
+  const int t = tunable(MDY_TUNE_NORM_FWD_THREADS);
+  return (t == 128 || t == 256 || t == 512) ? t : 256;
 }
 
 inline int64_t scalar_grid(int64_t M) {
@@ -406,18 +449,29 @@ inline int64_t scalar_grid(int64_t M) {
   return M < cap ? (M > 0 ? M : 1) : cap;
 }
 
+// Everything the backward launch derives from the problem size and the knobs, computed ONCE per call:
+// the entry point that checks a scratch size and the launch that follows must see the same grid.
+struct BwdPlan {
+  RowPlan p;      // p.vpt == 0: scalar kernel
+  int64_t grid;   // CTAs = partial rows written
+};
+
+template <typename T>
+inline BwdPlan plan_bwd(int64_t M, int64_t N, bool vec_ok) {
+  constexpr int VE = VecInfo<T>::kElems;
+  BwdPlan b{RowPlan{0, 0, 0, 0}, 0};
+  if (vec_ok && N % VE == 0)
+    b.p = plan_rows(N / VE, bwd_min_threads(), tunable(MDY_TUNE_NORM_BWD_VPT), tunable(MDY_TUNE_NORM_BWD_GROUP));
+  if (M == 0) b.grid = 0;
+  else b.grid = b.p.vpt ? vec_grid(M, b.p, bwd_per_sm(b.p)) : scalar_grid(M);
+  return b;
+}
+
+// Upper bound over both kernels (the caller sizes its scratch before alignment is known).
 template <typename T>
 inline int64_t partial_rows(int64_t M, int64_t N) {
-  constexpr int VE = VecInfo<T>::kElems;
-  int64_t rows = scalar_grid(M);
-  if (N % VE == 0) {
-    RowPlan p = plan_rows(N / VE, bwd_min_threads(), tunable(MDY_TUNE_NORM_BWD_VPT));
-    if (p.vpt) {
-      int64_t g = vec_grid(M, p, bwd_per_sm(p));
-      if (g > rows) rows = g;
-    }
-  }
-  return rows;
+  const int64_t a = plan_bwd<T>(M, N, true).grid, b = plan_bwd<T>(M, N, false).grid;
+  return a > b ? a : b;
 }
 
 template <typename T, bool ADD>
@@ -429,7 +483,9 @@ int launch_fwd(const void* x_, const void* res_, const void* w, int w_dtype, voi
   T* y = (T*)y_; T* nres = (T*)nres_;
   bool vec = N % VE == 0 && aligned16(x) && aligned16(y) && x_rs % VE == 0 && y_rs % VE == 0;
   if (ADD) vec = vec && aligned16(res) && aligned16(nres) && res_rs % VE == 0 && nres_rs % VE == 0;
-  RowPlan p = vec ? plan_rows(N / VE, 256, tunable(MDY_TUNE_NORM_FWD_VPT)) : RowPlan{0, 0, 0, 0};
+  RowPlan p = vec ? plan_rows(N / VE, fwd_min_threads(), tunable(MDY_TUNE_NORM_FWD_VPT), tunable(MDY_TUNE_NORM_FWD_GROUP))
+                  : RowPlan{0, 0, 0, 0};
+  const bool wvec = aligned16(w);
   if (p.vpt) {
     const int64_t grid = vec_grid(M, p, norm_ctas_per_sm() * (1024 / p.BT));
     const size_t sh = 2 * (p.BT / 32) * sizeof(float);
@@ -438,7 +494,7 @@ int launch_fwd(const void* x_, const void* res_, const void* w, int w_dtype, voi
 #define MDY_FWD(V, MT)                                                                           \
   norm_fwd_vec<T, V, ADD, MT><<<(unsigned)grid, p.BT, sh, st>>>(x, res, w, w_dtype, y, nres, rstd, \
                                                                 M, (int)N, x_rs, res_rs, y_rs,   \
-                                                                nres_rs, eps, p.G)
+                                                                nres_rs, eps, p.G, wvec)
     if (p.BT <= 512) {
       if (p.vpt == 1) MDY_FWD(1, 512); else if (p.vpt == 2) MDY_FWD(2, 512); else MDY_FWD(4, 512);
     } else {
@@ -456,27 +512,34 @@ int launch_fwd(const void* x_, const void* res_, const void* w, int w_dtype, voi
   return finish_launch(1);
 }
 
-template <typename T, bool ADD>
-int launch_bwd(const void* dy_, const void* x_, const void* w, int w_dtype, const float* rstd,
-               const void* dres_, void* dx_, void* dw, float* dw_partial, int64_t M, int64_t N,
-               int64_t dy_rs, int64_t x_rs, int64_t dres_rs, int64_t dx_rs, cudaStream_t st) {
+// Whether the 16-byte kernels can serve these buffers.
+template <typename T>
+inline bool bwd_vec_ok(const void* dy, const void* x, const void* dres, const void* dx, int64_t N, int64_t dy_rs,
+                       int64_t x_rs, int64_t dres_rs, int64_t dx_rs) {
   constexpr int VE = VecInfo<T>::kElems;
-  const T* dy = (const T*)dy_; const T* x = (const T*)x_;
-  const T* dres = (const T*)dres_; T* dx = (T*)dx_;
   bool vec = N % VE == 0 && aligned16(dy) && aligned16(x) && aligned16(dx) && dy_rs % VE == 0 &&
              x_rs % VE == 0 && dx_rs % VE == 0;
-  if (ADD && dres) vec = vec && aligned16(dres) && dres_rs % VE == 0;
-  RowPlan p = vec ? plan_rows(N / VE, bwd_min_threads(), tunable(MDY_TUNE_NORM_BWD_VPT)) : RowPlan{0, 0, 0, 0};
-  int64_t grid;
+  if (dres) vec = vec && aligned16(dres) && dres_rs % VE == 0;
+  return vec;
+}
+
+template <typename T, bool ADD>
+int launch_bwd(const BwdPlan& plan, const void* dy_, const void* x_, const void* w, int w_dtype, const float* rstd,
+               const void* dres_, void* dx_, void* dw, float* dw_partial, int64_t M, int64_t N,
+               int64_t dy_rs, int64_t x_rs, int64_t dres_rs, int64_t dx_rs, cudaStream_t st) {
+  const T* dy = (const T*)dy_; const T* x = (const T*)x_;
+  const T* dres = (const T*)dres_; T* dx = (T*)dx_;
+  const RowPlan& p = plan.p;
+  const int64_t grid = plan.grid;
+  const bool wvec = aligned16(w);
   if (M == 0) {
-    grid = 0;  // nothing to sweep: the reduce below writes dw = 0
+    // nothing to sweep: the reduce below writes dw = 0
   } else if (p.vpt) {
-    grid = vec_grid(M, p, bwd_per_sm(p));
     const size_t sh = (2 * (p.BT / 32) + (p.gpc > 1 ? N : 0)) * sizeof(float);
 #define MDY_BWD(V, MT)                                                                          \
   norm_bwd_vec<T, V, ADD, MT><<<(unsigned)grid, p.BT, sh, st>>>(dy, x, w, w_dtype, rstd, dres,  \
                                                                 dx, dw_partial, M, (int)N,      \
-                                                                dy_rs, x_rs, dres_rs, dx_rs, p.G)
+                                                                dy_rs, x_rs, dres_rs, dx_rs, p.G, wvec)
     if (p.BT <= 512) {
       if (p.vpt == 1) MDY_BWD(1, 512); else if (p.vpt == 2) MDY_BWD(2, 512); else MDY_BWD(4, 512);
     } else {
@@ -488,7 +551,6 @@ int launch_bwd(const void* dy_, const void* x_, const void* w, int w_dtype, cons
     }
 #undef MDY_BWD
   } else {
-    grid = scalar_grid(M);
     norm_bwd_scalar<T, ADD><<<(unsigned)grid, 256, 0, st>>>(dy, x, w, w_dtype, rstd, dres, dx,
                                                            dw_partial, M, N, dy_rs, x_rs, dres_rs,
                                                            dx_rs);
@@ -580,7 +642,8 @@ int mdy_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
   if (dy_row_stride < 0 || x_row_stride < N || dx_row_stride < N) return MDY_ERR_SIZE;
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
-    return launch_bwd<T, false>(dy, x, w, w_dtype, rstd, nullptr, dx, dw, dw_partial, M, N,
+    const BwdPlan plan = plan_bwd<T>(M, N, bwd_vec_ok<T>(dy, x, nullptr, dx, N, dy_row_stride, x_row_stride, 0, dx_row_stride));
+    return launch_bwd<T, false>(plan, dy, x, w, w_dtype, rstd, nullptr, dx, dw, dw_partial, M, N,
                                 dy_row_stride, x_row_stride, 0, dx_row_stride, (cudaStream_t)stream);
   });
 }
@@ -594,17 +657,18 @@ int mdy_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const 
   if (!dw || !w) return MDY_ERR_NULL;
   if (M > 0 && (!dy || !x || !rstd || !dx)) return MDY_ERR_NULL;
   if (dy_row_stride < 0 || x_row_stride < N || dx_row_stride < N) return MDY_ERR_SIZE;
-  // the partial-row scratch has a fixed size: refuse problems that would not fit
-  if (mdy_rmsnorm_bwd_partial_rows(M, N, dtype) * N > kNoAllocFloats) return MDY_ERR_UNSUPPORTED;
-  cudaError_t err;
-  float* scratch = noalloc_scratch(&err);
-  if (!scratch) {
-    (void)cudaGetLastError();
-    return err != cudaSuccess ? (int)err : MDY_ERR_ARG;
-  }
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
-    return launch_bwd<T, false>(dy, x, w, w_dtype, rstd, nullptr, dx, dw, scratch, M, N, dy_row_stride,
+    // the grid is fixed here, once, and the same value is checked against the scratch and launched
+    const BwdPlan plan = plan_bwd<T>(M, N, bwd_vec_ok<T>(dy, x, nullptr, dx, N, dy_row_stride, x_row_stride, 0, dx_row_stride));
+    if (plan.grid * N > kNoAllocFloats) return (int)MDY_ERR_UNSUPPORTED;  // would not fit the fixed scratch
+    cudaError_t err;
+    float* scratch = noalloc_scratch(&err);
+    if (!scratch) {
+      (void)cudaGetLastError();
+      return err != cudaSuccess ? (int)err : (int)MDY_ERR_ARG;
+    }
+    return launch_bwd<T, false>(plan, dy, x, w, w_dtype, rstd, nullptr, dx, dw, scratch, M, N, dy_row_stride,
                                 x_row_stride, 0, dx_row_stride, (cudaStream_t)stream);
   });
 }
@@ -634,7 +698,8 @@ int mdy_add_rmsnorm_bwd(const void* dy, const void* dnew_res, const void* new_re
   if (row_stride < N) return MDY_ERR_SIZE;
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
-    return launch_bwd<T, true>(dy, new_res, w, w_dtype, rstd, dnew_res, dx, dw, dw_partial, M, N,
+    const BwdPlan plan = plan_bwd<T>(M, N, bwd_vec_ok<T>(dy, new_res, dnew_res, dx, N, row_stride, row_stride, row_stride, row_stride));
+    return launch_bwd<T, true>(plan, dy, new_res, w, w_dtype, rstd, dnew_res, dx, dw, dw_partial, M, N,
                                row_stride, row_stride, row_stride, row_stride, (cudaStream_t)stream);
   });
 }

@@ -328,26 +328,22 @@ def test_swiglu_linearity_full_size():
 
 
 # ---------------------------------------------------------------------------------------- cross-entropy
-@pytest.fixture(params=["auto", "expcache512", "expcache1024", "reg512x8", "reg512x4", "smem", "smem1024x2", "smem256x8",
-                        "smem512x2_small_slices", "row"], autouse=False)
+@pytest.fixture(params=["auto", "smem1024x2", "smem256x8", "smem512x2_small_slices", "row"], autouse=False)
 def fused_impl(request):
-    """Run a test under every one-pass implementation: the default dispatch, the cluster kernel that
-    caches the exponentials in shared memory (two CTA sizes), the one that keeps them in registers, the
-    one that stages the whole slice and recomputes (default shape, two other CTA shapes, and 16 KB slices
-    that force clusters of up to 8 CTAs), and the row-per-CTA kernel all of them fall back to."""
+    """Run a test under every one-pass implementation: the default dispatch (the cluster kernel that stages
+    the row slice in shared memory), two other CTA shapes of it, 16 KB slices that force clusters of up to
+    8 CTAs, and the row-per-CTA kernel it falls back to."""
     name = request.param
-    impl = {"auto": 0, "row": 1, "expcache512": 4, "expcache1024": 4}.get(name, 2 if name.startswith("smem") else 3)
-    shape = {"reg512x8": 0, "reg512x4": 2, "expcache512": 1, "expcache1024": 2}.get(name, 0)
+    impl = 1 if name == "row" else 0
     nt, vpc, kb, minb = {"smem1024x2": (1024, 2, 0, 1), "smem256x8": (256, 8, 0, 2),
                          "smem512x2_small_slices": (512, 2, 16, 2)}.get(name, (0, 0, 0, 0))
     _C.set_tunable(_C.TUNE_CE_FUSED_IMPL, impl)
-    _C.set_tunable(_C.TUNE_CE_REG_SHAPE, shape)
     _C.set_tunable(_C.TUNE_CE_CLUSTER_THREADS, nt)
     _C.set_tunable(_C.TUNE_CE_CLUSTER_VPC, vpc)
     _C.set_tunable(_C.TUNE_CE_CLUSTER_SLICE_KB, kb)
     _C.set_tunable(_C.TUNE_CE_CLUSTER_MINB, minb)
     yield name
-    for t in (_C.TUNE_CE_FUSED_IMPL, _C.TUNE_CE_REG_SHAPE, _C.TUNE_CE_CLUSTER_THREADS, _C.TUNE_CE_CLUSTER_VPC,
+    for t in (_C.TUNE_CE_FUSED_IMPL, _C.TUNE_CE_CLUSTER_THREADS, _C.TUNE_CE_CLUSTER_VPC,
               _C.TUNE_CE_CLUSTER_SLICE_KB, _C.TUNE_CE_CLUSTER_MINB):
         _C.set_tunable(t, 0)
     torch.cuda.synchronize()
