@@ -2,6 +2,7 @@
 """Benchmark of the fused-operator path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--config c1|c2|c3]
+                    [--workload opset|llama1b|llama1b-unpatched|llama1b-fused-residual|vpce|op:NAME] [--no-extras]
 
 One step = forward + backward of the fused operator set at one benchmark config (default c2, the
 Llama-3-8B-shaped set: add+RMSNorm [32768,4096], RoPE 32q/8kv heads x 128, SwiGLU [32768,14336],
@@ -17,9 +18,20 @@ Printed JSON (rank 0, one line):
              host->device copies of every step's inputs and the device->host read of the loss are
              inside the timed region
   cpu_baseline  the float32 CPU oracle (HF-eager-equivalent math, autograd) on a bounded token sample
+and, unless --no-extras is given, further keys that do not change the headline:
+  configs    per-operator tables of the other two operator-set configurations (c1, c3)
+  token_parallel_with_allreduce  the same step followed by the all-reduce a token-sharded caller needs
+             (the RMSNorm weight gradient [hidden] and the loss sum / token count), N > 1 only
+  vpce       the vocab-parallel cross-entropy sweep over the N ranks, collective inside the timed region,
+             with an on-device check of every case against the full-vocabulary one-GPU loss
+  llama1b_train_step  the patched Llama-1B training step (DDP over the N ranks)
+  triton_reference    the reference's own Triton kernels timed by the same CUDA-event harness on the same
+             tensors (N = 1 only; outside every timed region of this library's kernels)
 
 `--impl reference` times the CPU oracle only (the reference has no CPU implementation of its own; its
-Triton kernels need a GPU and its sources do not travel to the benchmark machine).
+Triton kernels need a GPU and are reported under `triton_reference` of the default arm).
+`--workload op:NAME` (NAME in norm, rmsnorm, rope, swiglu, ce, ce2, vp) runs ONE operator forward+backward
+a few times and prints its time: the small program profiler captures are taken from.
 """
 from __future__ import annotations
 
@@ -52,6 +64,7 @@ OPS = ("norm", "rope", "swiglu", "cross_entropy")
 PHASES = (("norm", "fwd", "norm_fwd"), ("norm", "bwd", "norm_bwd"), ("rope", "fwd", "rope_fwd"), ("rope", "bwd", "rope_bwd"),
           ("swiglu", "fwd", "swiglu_fwd"), ("swiglu", "bwd", "swiglu_bwd"), ("cross_entropy", "fwd+bwd", "cross_entropy"))
 FALLBACK_PEAK_GBS = 6650.0
+NOMINAL_HBM_GBS = 7700.0   # HGX B200 data-sheet figure, reported beside the measured copy bandwidth
 # dram__bytes_read.sum + dram__bytes_write.sum of one one-pass cross-entropy launch, from the ncu capture
 # summarised under profiles/ (None until a capture exists): bytes per row of the captured case.
 CE_TRAFFIC_BYTES_PER_ROW = 499109
@@ -77,7 +90,7 @@ def measured_peak():
             return float(json.loads(p.read_text())["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
         except Exception:
             pass
-    return FALLBACK_PEAK_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+    return FALLBACK_PEAK_GBS, "fallback (no MEASURED_PEAKS.json beside bench.py)"
 
 
 # ------------------------------------------------------------------------------------------------ clocks
@@ -531,23 +544,37 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
 
 
 # ------------------------------------------------------------------------------ vocab-parallel CE sweep
-def run_vpce(dev, dist, world, rank, steps, warmup):
+VPCE_TOKENS = 16384
+VPCE_VOCABS = (32000, 128256, 151936, 256000)
+VPCE_SIGMAS = (1.0, 4.0)
+
+
+def _vpce_shard(dev, M, vs, sigma, r):
+    g = torch.Generator(dev).manual_seed(3 + r)
+    return torch.randn(M, vs, device=dev, dtype=torch.bfloat16, generator=g).mul_(sigma)
+
+
+def run_vpce(dev, dist, world, rank, steps, warmup, check=True):
     """Vocab-parallel sweep: 16384 tokens, vocab in {32000, 128256, 151936, 256000} sharded over the ranks,
     logits N(0, sigma^2) with sigma in {1, 4}, 5 % of the labels -100, bf16, gradient written in place.
     Per step and rank: local sweep (mdy_ce_fwd, split mode) -> one all_gather of [2, M] float32 ->
-    mdy_ce_vp_combine -> local gradient sweep (mdy_ce_bwd).  The collective is inside the timed region."""
+    mdy_ce_vp_combine -> local gradient sweep (mdy_ce_bwd).  The collective is inside the timed region.
+    With `check`, every case's loss is compared on the device with the loss the one-pass kernel gives on the
+    full vocabulary (all shards side by side on this GPU): they must agree to 1e-4."""
     from mdy_triton_b200.core import vocab_parallel as vp
-    M = 16384
+    import mdy_triton.core as core
+    M = VPCE_TOKENS
     cases = []
-    for V in (32000, 128256, 151936, 256000):
-        for sigma in (1.0, 4.0):
+    parity = "ok"
+    for V in VPCE_VOCABS:
+        for sigma in VPCE_SIGMAS:
             vs = V // world
-            g = torch.Generator(dev).manual_seed(3 + rank)
-            shard = torch.randn(M, vs, device=dev, dtype=torch.bfloat16, generator=g).mul_(sigma)
+            shard = _vpce_shard(dev, M, vs, sigma, rank)
             gl = torch.Generator(dev).manual_seed(3)                       # labels identical on every rank
             labels = torch.randint(0, vs * world, (M,), device=dev, generator=gl)
             labels[torch.rand(M, device=dev, generator=gl) < 0.05] = -100
             f_ign = float((labels == -100).float().mean())
+            n_valid = (labels != -100).sum()
             dl = torch.full((M,), 1.0 / M, device=dev)
             stats = torch.empty(2, M, dtype=torch.float32, device=dev)
             gathered = torch.empty(world, 2, M, dtype=torch.float32, device=dev)
@@ -578,16 +605,222 @@ def run_vpce(dev, dist, world, rank, steps, warmup):
                 tt = torch.tensor([t], dtype=torch.float64, device=dev)
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
                 t = float(tt[0])
+            loss = float(losses.sum() / n_valid)
+            case = {"vocab": vs * world, "sigma": sigma, "ms": t}
             alg = M * vs * 2 * (2 - f_ign) * world
-            moved = M * vs * 2 * (3 - 2 * f_ign) * world
-            cases.append({"vocab": vs * world, "sigma": sigma, "ms": t, "algorithmic_GBps": alg / t / 1e6,
-                          "moved_GBps": moved / t / 1e6, "loss": float(losses.sum() / (labels != -100).sum())})
-            del shard, work
+            case.update({"algorithmic_GBps": alg / t / 1e6, "loss": loss})
+            del work
+            if check:
+                # the same logits as ONE [M, V] tensor on this GPU, through the one-pass full-vocabulary kernel
+                full = torch.empty(M, vs * world, device=dev, dtype=torch.bfloat16)
+                for r in range(world):
+                    full[:, r * vs:(r + 1) * vs] = shard if r == rank else _vpce_shard(dev, M, vs, sigma, r)
+                full.requires_grad_(True)
+                ref = core.triton_entropy_loss(full, labels)
+                ref.backward()
+                # and this rank's gradient against the matching columns of the full-vocabulary gradient
+                work2 = shard.clone()
+                vp._local_forward(work2, labels, vs * rank, stats)
+                if dist is not None:
+                    dist.all_gather_into_tensor(gathered.view(-1), stats.view(-1))
+                else:
+                    gathered[0].copy_(stats)
+                _, lse = vp._combine(gathered, labels)
+                dn = torch.full((M,), 1.0, device=dev) / n_valid
+                vp._local_backward(dn, work2, labels, lse, work2, vs * rank)
+                want = full.grad[:, rank * vs:(rank + 1) * vs].float()
+                err = (work2.float() - want).abs()
+                grad_ok = bool((err <= 1e-2 * (want.abs() + want.abs().mean())).all())
+                del work2, want, err
+                case["full_vocab_loss"] = float(ref)
+                ok = abs(loss - float(ref)) <= 1e-4 * max(1.0, abs(float(ref))) and grad_ok
+                if dist is not None:
+                    flag = torch.tensor([0 if ok else 1], device=dev)
+                    dist.all_reduce(flag)
+                    ok = int(flag[0]) == 0
+                if not ok:
+                    parity = f"MISMATCH at vocab {V} sigma {sigma}: {loss} vs {float(ref)}, gradient ok: {grad_ok}"
+                del full, ref
+            cases.append(case)
+            del shard
             torch.cuda.empty_cache()
-    return cases
+    return cases, parity
+
+
+def vpce_summary(cases, parity, world, peak):
+    val = statistics.mean(c["algorithmic_GBps"] for c in cases)
+    for c in cases:
+        c["frac_of_peak_per_gpu"] = c["algorithmic_GBps"] / world / peak
+    return {"metric": "vocab_parallel_ce_fwd_bwd_algorithmic_hbm_throughput", "value": val, "unit": "GB/s",
+            "scaling": "strong", "tokens": VPCE_TOKENS, "frac_of_peak_per_gpu": val / world / peak,
+            "parity": parity, "parity_check": "each case: loss and this rank's gradient columns against the one-pass kernel on "
+            "the full vocabulary on one GPU (1e-4 on the loss, 1e-2 relative on the gradient)",
+            "workload": "16384 tokens, vocab sharded over the GPUs, per-row statistics exchanged inside the timed region, "
+                        "gradient in place", "cases": cases}
+
+
+# -------------------------------------------------------------------------------- one operator at a time
+def run_single_op(args):
+    """`--workload op:NAME`: forward + backward of ONE operator a few times on synthetic bf16 tensors of the
+    chosen configuration's shapes (`--tokens` rows, `--vocab` / `--hidden` override the row length) and the
+    CUDA-event time per iteration.  A small program for profiler captures and for trying launch-shape knobs
+    (`--tune ID=VALUE`, ids in mdy_triton_b200/csrc/tunables.h); with `--flush` a 256 MB buffer is overwritten
+    before every launch so inputs smaller than the L2 come from HBM (its time is measured and subtracted)."""
+    from mdy_triton_b200 import _C
+    op = args.workload[3:]
+    for t in args.tune:
+        tid, val = t.split("=")
+        _C.set_tunable(int(tid), int(val))
+    cfg = dict(CONFIGS[args.config])
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    lib = _C.lib()
+    st = torch.cuda.current_stream().cuda_stream
+    bf = _C.MDY_BF16
+    g = torch.Generator(dev).manual_seed(1)
+    M = args.tokens or 16384
+    iters = max(1, args.steps)
+
+    def rn(*shape):
+        return torch.randn(*shape, device=dev, dtype=torch.bfloat16, generator=g)
+
+    if op in ("norm", "rmsnorm"):
+        N = args.hidden or cfg["hidden"]
+        x, res, dy, dn, w = rn(M, N), rn(M, N), rn(M, N), rn(M, N), rn(N)
+        y, nres, dx, dw = torch.empty_like(x), torch.empty_like(x), torch.empty_like(x), torch.empty_like(w)
+        rstd = torch.empty(M, device=dev)
+        part = torch.empty(lib.mdy_rmsnorm_bwd_partial_rows(M, N, bf), N, device=dev)
+        if op == "norm":
+            phases = [lambda: _C.check(lib.mdy_add_rmsnorm_fwd(x.data_ptr(), res.data_ptr(), w.data_ptr(), y.data_ptr(), nres.data_ptr(),
+                                                               rstd.data_ptr(), M, N, N, 1e-5, bf, bf, st), "fwd"),
+                      lambda: _C.check(lib.mdy_add_rmsnorm_bwd(dy.data_ptr(), dn.data_ptr(), nres.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                                                               dx.data_ptr(), dw.data_ptr(), part.data_ptr(), M, N, N, bf, bf, st), "bwd")]
+            nbytes = [4 * M * N * 2, 4 * M * N * 2]
+        else:
+            phases = [lambda: _C.check(lib.mdy_rmsnorm_fwd(x.data_ptr(), w.data_ptr(), y.data_ptr(), rstd.data_ptr(), M, N, N, N, 1e-5, bf,
+                                                           bf, st), "fwd"),
+                      lambda: _C.check(lib.mdy_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                                           dw.data_ptr(), part.data_ptr(), M, N, N, N, N, bf, bf, st), "bwd")]
+            nbytes = [2 * M * N * 2, 3 * M * N * 2]
+    elif op == "rope":
+        L, QH, KH, D = cfg["L"], cfg["QH"], cfg["KH"], cfg["D"]
+        B = max(1, M // L)
+        q, k, dq, dk = rn(B, L, QH, D), rn(B, L, KH, D), rn(B, L, QH, D), rn(B, L, KH, D)
+        dqo, dko = torch.empty_like(q), torch.empty_like(k)
+        cos, sin = rn(1, L, D), rn(1, L, D)
+        sq = (q.stride(0), q.stride(2), q.stride(1)); sk = (k.stride(0), k.stride(2), k.stride(1))
+        phases = [lambda: _C.check(lib.mdy_rope(q.data_ptr(), q.data_ptr(), k.data_ptr(), k.data_ptr(), cos.data_ptr(), sin.data_ptr(), B, L,
+                                                QH, KH, D, 1, *sq, *sq, *sk, *sk, 0, bf, st), "fwd"),
+                  lambda: _C.check(lib.mdy_rope(dq.data_ptr(), dqo.data_ptr(), dk.data_ptr(), dko.data_ptr(), cos.data_ptr(), sin.data_ptr(),
+                                                B, L, QH, KH, D, 1, *sq, *sq, *sk, *sk, 1, bf, st), "bwd")]
+        nbytes = [2 * B * L * (QH + KH) * D * 2 + 2 * L * D * 2] * 2
+    elif op == "swiglu":
+        N = args.hidden or cfg["ffn"]
+        up, gate, dy = rn(M, N), rn(M, N), rn(M, N)
+        y, dup, dgate = torch.empty_like(up), torch.empty_like(up), torch.empty_like(up)
+        phases = [lambda: _C.check(lib.mdy_swiglu_fwd(up.data_ptr(), gate.data_ptr(), y.data_ptr(), M, N, N, N, N, bf, st), "fwd"),
+                  lambda: _C.check(lib.mdy_swiglu_bwd(dy.data_ptr(), up.data_ptr(), gate.data_ptr(), dup.data_ptr(), dgate.data_ptr(), M, N,
+                                                      N, N, N, N, N, bf, st), "bwd")]
+        nbytes = [3 * M * N * 2, 5 * M * N * 2]
+    elif op == "ce2":
+        V = args.vocab or cfg["vocab"]
+        lg = rn(M, V).mul_(3)
+        lb = torch.randint(0, V, (M,), device=dev, generator=g)
+        losses = torch.empty(M, device=dev); lse = torch.empty(M, device=dev); dl = torch.ones(M, device=dev)
+        phases = [lambda: _C.check(lib.mdy_ce_fwd(lg.data_ptr(), lb.data_ptr(), losses.data_ptr(), lse.data_ptr(), M, V, V, 0, 0, bf, st), "fwd"),
+                  lambda: _C.check(lib.mdy_ce_bwd(dl.data_ptr(), 1, 0, lg.data_ptr(), lg.data_ptr(), lb.data_ptr(), lse.data_ptr(), M, V, V,
+                                                  0, 1, bf, st), "bwd")]
+        nbytes = [M * V * 2, 2 * M * V * 2]
+    elif op == "ce":
+        V = args.vocab or cfg["vocab"]
+        lg = rn(M, V).mul_(3)
+        lb = torch.randint(0, V, (M,), device=dev, generator=g)
+        out = torch.empty_like(lg); losses = torch.empty(M, device=dev); lse = torch.empty(M, device=dev)
+        inv = torch.tensor([1.0 / M], device=dev)
+        phases = [lambda: _C.check(lib.mdy_ce_fused(lg.data_ptr(), out.data_ptr(), lb.data_ptr(), losses.data_ptr(), lse.data_ptr(),
+                                                    inv.data_ptr(), 1.0, M, V, V, bf, st), "ce")]
+        nbytes = [2 * M * V * 2]
+    else:
+        raise SystemExit(f"unknown operator {op!r}")
+
+    buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev) if args.flush else None
+
+    def timed(fn):
+        fn()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            if buf is not None:
+                buf.fill_(1)
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters * 1e3
+
+    base = timed(lambda: None) if buf is not None else 0.0
+    res = {"op": op, "rows": M, "flush": bool(args.flush), "tune": args.tune, "phases": []}
+    for fn, nb in zip(phases, nbytes):
+        us = timed(fn) - base
+        res["phases"].append({"us": round(us, 2), "GBps": round(nb / us / 1e3, 1)})
+    res["device_GB"] = round(torch.cuda.memory_allocated(dev) / 1e9, 2)
+    print(json.dumps(res))
 
 
 # -------------------------------------------------------------------------------------------------- main
+def compact_table(cfg, dev, seed, steps, warmup, barrier, max_over_ranks, peak, rank, graph_replay=True):
+    """Per-operator figures of one more operator-set configuration: ms, algorithmic GB/s, fraction of the
+    measured peak, forward and backward apart."""
+    ops = OpSet(cfg, dev, seed)
+    flush = needs_l2_flush(cfg)
+    ab = algorithmic_bytes(cfg, ops.M, ops.ignored_frac)
+    total_ms, phase_ms, _ = run_device_arm(ops, steps, warmup, barrier, flush)
+    per_op_ms = {n: sum(ms for (op, _, _), ms in zip(PHASES, phase_ms) if op == n) for n in OPS}
+    ms_per_step = max_over_ranks(total_ms) / steps
+    table = {"workload": cfg["desc"], "tokens_per_gpu": ops.M, "l2_flushed": flush, "ms_per_step": ms_per_step,
+             "GB/s_per_gpu": sum(ab.values()) / (ms_per_step * 1e-3) / 1e9,
+             "frac_of_peak": sum(ab.values()) / (ms_per_step * 1e-3) / 1e9 / peak, "per_op": {}}
+    for n in OPS:
+        gbs = ab[n] / (per_op_ms[n] * 1e-3) / 1e9
+        table["per_op"][n] = {"ms": per_op_ms[n], "GB/s": gbs, "frac_of_peak": gbs / peak}
+    for (op, direction, _), ms in zip(PHASES, phase_ms):
+        if direction in ("fwd", "bwd"):
+            table["per_op"][op][direction + "_ms"] = ms
+    table["per_op"]["norm"]["kind"] = cfg["norm"]
+    if flush and graph_replay and rank == 0:
+        for (op, direction, _), us in zip(PHASES, run_graph_replay(ops)):
+            table["per_op"][op].setdefault("graph_replay_us", {})[direction] = us
+    del ops
+    torch.cuda.empty_cache()
+    return table
+
+
+def run_with_allreduce(ops, dist, steps, warmup):
+    """The token-sharded step followed by what a caller that shards tokens must still exchange: ONE all-reduce
+    of a float32 vector holding the RMSNorm weight gradient [hidden], the loss sum and the valid-token count."""
+    H = ops.cfg["hidden"]
+    packed = torch.zeros(H + 2, dtype=torch.float32, device=ops.dev)
+
+    def step():
+        ops.step()
+        packed[:H].copy_(ops.dw)
+        packed[H] = ops.losses.sum()
+        packed[H + 1] = 1.0 / ops.inv_n[0]
+        dist.all_reduce(packed)
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        step()
+    t1.record()
+    torch.cuda.synchronize()
+    dist.barrier()
+    return t0.elapsed_time(t1) / steps
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -597,22 +830,30 @@ def main():
     ap.add_argument("--config", default="c2", choices=sorted(CONFIGS))
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="print the headline line only (no configs / vpce / llama1b_train_step / triton_reference keys)")
     ap.add_argument("--cpu-tokens", type=int, default=8192)
-    ap.add_argument("--workload", default="opset", choices=["opset", "llama1b", "llama1b-fused-residual", "llama1b-unpatched", "vpce"],
-                    help="opset (default): the fused operator set; llama1b: only the Llama-1B training step with "
-                         "the patch; llama1b-fused-residual: the same with each layer's closing residual add fused "
-                         "into the next RMSNorm; llama1b-unpatched: the same with stock HuggingFace modules")
+    ap.add_argument("--workload", default="opset",
+                    help="opset (default): the fused operator set; llama1b: only the Llama-1B training step with the patch; "
+                         "llama1b-fused-residual: the same with each layer's closing residual add fused into the next RMSNorm; "
+                         "llama1b-unpatched: the same with stock HuggingFace modules; vpce: only the vocab-parallel sweep; "
+                         "op:NAME: one operator (norm, rmsnorm, rope, swiglu, ce, ce2)")
     ap.add_argument("--profile-share", action="store_true",
                     help="llama1b workloads: after timing, profile two more steps and report the share of GPU kernel time spent in the fused kernels")
-    ap.add_argument("--ddp-bucket-mb", type=int, default=200,
-                    help="DDP gradient bucket size for the llama1b workloads (measured at 8 GPUs: 25 MB 825.6k, 100 MB 837.2k, "
-                         "200 MB 842.3k tokens/s)")
-    ap.add_argument("--train-step", action="store_true",
-                    help="after the operator set, also time the patched Llama-1B training step (adds ~1 min)")
+    ap.add_argument("--ddp-bucket-mb", type=int, default=200, help="DDP gradient bucket size for the llama1b workloads")
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the tokens per GPU (a multiple of the config's sequence length); smaller "
                          "cases are for profiler captures, not for reported numbers")
+    ap.add_argument("--vocab", type=int, default=0, help="op:ce / op:ce2: row length")
+    ap.add_argument("--hidden", type=int, default=0, help="op:norm / op:rmsnorm / op:swiglu: row length")
+    ap.add_argument("--tune", action="append", default=[], metavar="ID=VALUE", help="op:NAME: set a launch-shape knob")
+    ap.add_argument("--flush", action="store_true", help="op:NAME: flush the L2 before every launch")
     args = ap.parse_args()
+    if args.workload.startswith("op:"):
+        run_single_op(args)
+        return
+    if args.workload not in ("opset", "llama1b", "llama1b-fused-residual", "llama1b-unpatched", "vpce"):
+        raise SystemExit(f"unknown workload {args.workload!r}")
     cfg = dict(CONFIGS[args.config])
     if args.tokens:
         if args.tokens % cfg["L"]:
@@ -663,16 +904,14 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])
 
+    peak, peak_src = measured_peak()
     if args.workload == "vpce":
-        cases = run_vpce(dev, dist, world, rank, max(3, min(args.steps, 10)), 3)
+        cases, parity = run_vpce(dev, dist, world, rank, max(3, min(args.steps, 10)), 3)
         if rank == 0:
-            peak, _ = measured_peak()
-            val = statistics.mean(c["algorithmic_GBps"] for c in cases)
-            print(json.dumps({"metric": "vocab_parallel_ce_fwd_bwd_algorithmic_hbm_throughput", "value": val, "unit": "GB/s",
-                              "n_gpus": world, "higher_is_better": True, "scaling": "strong", "dtype": "bf16", "data": "synthetic",
-                              "config": {"workload": "vocab-parallel cross-entropy sweep, 16384 tokens, vocab sharded over the GPUs, "
-                                         "one all-gather of per-row statistics inside the timed region, gradient in place"},
-                              "frac_of_peak_per_gpu": val / world / peak, "cases": cases}))
+            out = vpce_summary(cases, parity, world, peak)
+            out.update({"n_gpus": world, "higher_is_better": True, "dtype": "bf16", "data": "synthetic",
+                        "config": {"workload": "vocab-parallel cross-entropy sweep: " + out.pop("workload")}})
+            print(json.dumps(out))
         if dist is not None:
             dist.destroy_process_group()
         return
@@ -702,9 +941,9 @@ def main():
     total_ms = max_over_ranks(total_ms)
     ms_per_step = total_ms / args.steps
     value = world * step_bytes / (ms_per_step * 1e-3) / 1e9
-    peak, peak_src = measured_peak()
     per_op = {n: {"ms": per_op_ms[n], "GB/s": ab[n] / (per_op_ms[n] * 1e-3) / 1e9,
-                  "frac_of_peak": ab[n] / (per_op_ms[n] * 1e-3) / 1e9 / peak, "algorithmic_bytes": ab[n]} for n in OPS}
+                  "frac_of_peak": ab[n] / (per_op_ms[n] * 1e-3) / 1e9 / peak,
+                  "frac_of_nominal": ab[n] / (per_op_ms[n] * 1e-3) / 1e9 / NOMINAL_HBM_GBS, "algorithmic_bytes": ab[n]} for n in OPS}
     for (op, direction, _), ms in zip(PHASES, phase_ms):
         if direction in ("fwd", "bwd"):
             per_op[op][direction + "_ms"] = ms
@@ -720,20 +959,58 @@ def main():
                "d2h_bytes_per_step": d2h, "ms_per_step": e_ms, "loss": loss}
 
     clocks = sampler.stop() if rank == 0 else None  # sampled over both timed regions (device arm and e2e arm)
+    extras = {}
+    extras_on = not args.no_extras and not args.tokens
+
+    def guarded(name, fn):
+        """An extra leg must never cost the headline line: its failure is recorded under its key."""
+        try:
+            extras[name] = fn()
+        except Exception as e:  # noqa: BLE001
+            extras[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+            torch.cuda.empty_cache()
+
+    if extras_on and dist is not None:
+        def with_allreduce():
+            ms = max_over_ranks(run_with_allreduce(ops, dist, min(args.steps, 10), 3))
+            return {"ms_per_step": ms, "value": world * step_bytes / (ms * 1e-3) / 1e9, "unit": unit,
+                    "without_allreduce_ms_per_step": ms_per_step,
+                    "collective": f"one all_reduce(SUM) of {cfg['hidden'] + 2} float32 per step (RMSNorm weight gradient, loss sum, token count)"}
+        guarded("token_parallel_with_allreduce", with_allreduce)
+    if extras_on and world == 1 and rank == 0:
+        def triton_reference():
+            from oracle import ref_loader, ref_timing
+            if not ref_loader.available():
+                return {"unavailable": "the reference's kernel files are not staged (python -m oracle.make_ref)"}
+            table = ref_timing.time_reference_ops(ops, iters=5, warmup=2, flush=flush)
+            for n, row in table.items():
+                ours = per_op["cross_entropy" if n.startswith("cross_entropy") else n]["ms"]
+                row["ours_ms"] = ours
+                row["speedup"] = row["ms"] / ours
+            return {"what": "the reference's Triton kernels (JIT-compiled by the installed Triton for this GPU) through the "
+                            "reference's own autograd-function host code, same tensors, CUDA events, median of 5",
+                    "per_op": table}
+        guarded("triton_reference", triton_reference)
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         gbs, dt, M, cores = run_cpu_baseline(cfg, args.cpu_tokens, 2, 1, cfg["seed"])
         cpu = {"value": gbs, "unit": unit, "cores": cores, "kind": "port",
                "sample": f"{M} of {n_rows} tokens, all four ops fwd+bwd, float32 autograd on host, {dt:.2f} s per pass"}
 
-    train = None
-    if args.train_step:
-        del ops
-        torch.cuda.empty_cache()
-        try:
-            train = run_llama1b(dev, dist, world, 5, 2, patched=True)
-        except Exception as e:  # noqa: BLE001 - the operator-set line must survive a failure here
-            train = {"error": f"{type(e).__name__}: {e}"[:300]}
+    del ops
+    torch.cuda.empty_cache()
+    if extras_on:
+        def other_configs():
+            return {name: compact_table(dict(CONFIGS[name]), dev, CONFIGS[name]["seed"] + rank, 10, 3, barrier, max_over_ranks,
+                                        peak, rank) for name in sorted(CONFIGS) if name != args.config}
+        guarded("configs", other_configs)
+
+        def vpce():
+            cases, parity = run_vpce(dev, dist, world, rank, 5, 3)
+            return vpce_summary(cases, parity, world, peak)
+        guarded("vpce", vpce)
+        guarded("llama1b_train_step", lambda: run_llama1b(dev, dist, world, 5, 2, patched=True, ddp_bucket_mb=args.ddp_bucket_mb))
 
     if rank == 0:
         ce = per_op["cross_entropy"]
@@ -749,8 +1026,7 @@ def main():
             out["e2e"] = e2e
         if cpu is not None:
             out["cpu_baseline"] = cpu
-        if train is not None:
-            out["llama1b_train_step"] = train
+        out.update(extras)
         print(json.dumps(out))
     if dist is not None:
         dist.destroy_process_group()

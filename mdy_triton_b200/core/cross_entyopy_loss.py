@@ -9,10 +9,15 @@ the reference file no longer defines; it is provided here with the same meaning 
 Two execution paths:
   * per-row API (``_FastCrossEntropyLoss.apply``): forward sweep writes ``losses``/``lse``, backward
     sweep writes ``dlogits`` from an arbitrary per-row upstream gradient — same contract as the reference.
-  * scalar-loss API (``triton_entropy_loss`` / ``fast_cross_entropy_loss``) with gradients enabled: the
-    gradient of ``sum(losses) / n_items`` w.r.t. each row is the constant ``1 / n_items``, known before
-    the kernel starts, so ONE kernel computes the loss and writes ``dlogits`` in a single pass over the
-    logits; backward only rescales if the incoming gradient is not 1.
+  * scalar-loss API (``triton_entropy_loss`` / ``fast_cross_entropy_loss``) with gradients enabled, for
+    bfloat16 and float32 logits: the gradient of ``sum(losses) / n_items`` w.r.t. each row is the constant
+    ``1 / n_items``, known before the kernel starts, so ONE kernel computes the loss and writes ``dlogits``
+    in a single pass over the logits; backward only rescales if the incoming gradient is not 1.  That
+    gradient buffer can be handed out once: a second backward through the same loss raises.
+    float16 logits and ``inplace=True`` take the per-row path instead: with a loss scaler the product
+    ``dloss * (softmax - onehot)`` has to be formed in float32 before it is rounded to float16 (the
+    unscaled ``(softmax - onehot) / n_items`` of a rare token underflows there), and in-place callers expect
+    their logits to stay intact until backward, as in the reference.
 """
 from __future__ import annotations
 
@@ -119,10 +124,16 @@ class _FusedLossAndGrad(torch.autograd.Function):
                                            _C.stream_ptr(dev)), "mdy_ce_fused")
         ctx.save_for_backward(dlogits)
         ctx.input_shape = logits.shape
+        ctx.consumed = False
         return losses.sum() * inv[0]
 
     @staticmethod
     def backward(ctx, dloss):
+        if ctx.consumed:
+            raise RuntimeError("the one-pass cross-entropy hands its gradient buffer out once: a second backward "
+                               "through the same loss would rescale the gradient it already returned; recompute the "
+                               "loss, or use _FastCrossEntropyLoss.apply for a graph that is walked twice")
+        ctx.consumed = True
         (dlogits,) = ctx.saved_tensors
         dev = dlogits.device
         g = dloss.detach().to(device=dev, dtype=torch.float32).reshape(1).contiguous()
@@ -140,7 +151,12 @@ def triton_entropy_loss(logits, labels, num_items_in_batch=None, inplace=None):
     if inplace is None:
         inplace = INPLACE_DEFAULT
     if torch.is_grad_enabled() and logits.requires_grad:
-        return _FusedLossAndGrad.apply(logits, labels, num_items_in_batch, bool(inplace))
+        if logits.dtype != torch.float16 and not inplace:
+            return _FusedLossAndGrad.apply(logits, labels, num_items_in_batch, False)
+        losses = _FastCrossEntropyLoss.apply(logits, labels, bool(inplace))
+        if num_items_in_batch is None:
+            num_items_in_batch = torch.count_nonzero(labels != IGNORE_INDEX)
+        return losses.sum() / num_items_in_batch
     lg, lb = _flat(logits, labels)
     losses, _ = ce_forward_rows(lg, lb)
     if num_items_in_batch is None:

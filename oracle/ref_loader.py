@@ -1,10 +1,16 @@
-"""Run the reference's own Triton kernels on CPU (Triton interpreter).  Test infrastructure only.
+"""Run the reference's own Triton kernels: on CPU under Triton's interpreter, on a GPU natively.
+Test infrastructure only.
 
 The reference package cannot be imported as a package (its ``core/__init__.py`` imports a name its
-loss module no longer defines), so each kernel file is loaded by path from a reference checkout
-(its path comes from ``MDY_REFERENCE_ROOT``; the default is the checkout's usual mount point).  Nothing is copied into this
-repository: a patched copy of each file is written to a temporary directory because Triton's JIT needs
-a source file, with only these host-side shims, none of which touches kernel arithmetic:
+loss module no longer defines), so each kernel file is loaded by path from ``oracle/_ref/``, where
+``oracle/make_ref.py`` stages unmodified copies of them (git-ignored; they travel with the working tree to
+the GPU machine but never enter the history).
+
+On a GPU (CUDA available and ``TRITON_INTERPRET`` not set to 1) the files are loaded exactly as staged
+and Triton's JIT compiles the kernels for the device: this is the reference running natively.
+
+Without a GPU a patched copy of each file is written to a temporary directory because Triton's JIT needs a
+source file, with only these host-side shims, none of which touches kernel arithmetic:
 
   * ``TRITON_INTERPRET=1`` (must be set before ``triton`` is first imported in the process);
   * the ``@triton.autotune`` decorators of ``core/rmsnorm.py`` are removed (the autotuner needs a GPU
@@ -13,8 +19,8 @@ a source file, with only these host-side shims, none of which touches kernel ari
     call (the host code asks for the SM count and enters a device context);
   * Python bools passed as non-constexpr kernel arguments are wrapped in ``int()``.
 
-Where the checkout is absent (the GPU machine), ``available()`` is False and callers use the golden
-vectors in ``tests/golden/`` instead.
+Where nothing is staged, ``available()`` is False and callers use the golden vectors in
+``tests/golden/`` instead.
 """
 from __future__ import annotations
 
@@ -27,14 +33,19 @@ import tempfile
 import types
 from pathlib import Path
 
-REFERENCE_ROOT = Path(os.environ.get("MDY_REFERENCE_ROOT", "/root/reference"))
-_CORE = REFERENCE_ROOT / "mdy_triton" / "core"
+_CORE = Path(__file__).resolve().parent / "_ref"
 _cache: dict[str, types.ModuleType] = {}
 _tmpdir = None
 
 
 def available() -> bool:
     return (_CORE / "rmsnorm.py").exists()
+
+
+def native() -> bool:
+    """True when the kernels run on a GPU through Triton's JIT (no interpreter, no shims)."""
+    import torch
+    return torch.cuda.is_available() and os.environ.get("TRITON_INTERPRET") != "1"
 
 
 def _prepare_env():
@@ -56,18 +67,20 @@ def _patch(name: str, src: str) -> str:
 
 
 def load(name: str) -> types.ModuleType:
-    """Load ``mdy_triton/core/<name>.py`` of the reference as an independent module."""
+    """Load the staged ``mdy_triton/core/<name>.py`` of the reference as an independent module."""
     global _tmpdir
     if name in _cache:
         return _cache[name]
     if not available():
-        raise FileNotFoundError(f"no reference checkout at {REFERENCE_ROOT}")
-    _prepare_env()
-    if _tmpdir is None:
-        _tmpdir = tempfile.TemporaryDirectory(prefix="mdy_ref_")
-    src = _patch(name, (_CORE / f"{name}.py").read_text())
-    path = Path(_tmpdir.name) / f"ref_{name}.py"
-    path.write_text(src)
+        raise FileNotFoundError(f"no staged reference kernels in {_CORE} (run python -m oracle.make_ref)")
+    if native():
+        path = _CORE / f"{name}.py"
+    else:
+        _prepare_env()
+        if _tmpdir is None:
+            _tmpdir = tempfile.TemporaryDirectory(prefix="mdy_ref_")
+        path = Path(_tmpdir.name) / f"ref_{name}.py"
+        path.write_text(_patch(name, (_CORE / f"{name}.py").read_text()))
     spec = importlib.util.spec_from_file_location(f"ref_{name}", path)
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
@@ -77,8 +90,12 @@ def load(name: str) -> types.ModuleType:
 
 @contextlib.contextmanager
 def cpu_shims(num_sms: int = 4):
-    """Let the reference's host code run without a GPU (see module docstring)."""
+    """Let the reference's host code run without a GPU (see module docstring); nothing is touched when the
+    kernels run natively."""
     import torch
+    if native():
+        yield
+        return
     old_dev, old_props = torch.cuda.device, torch.cuda.get_device_properties
     torch.cuda.device = lambda *a, **k: contextlib.nullcontext()
     torch.cuda.get_device_properties = lambda *a, **k: types.SimpleNamespace(multi_processor_count=num_sms)
@@ -88,7 +105,8 @@ def cpu_shims(num_sms: int = 4):
         torch.cuda.device, torch.cuda.get_device_properties = old_dev, old_props
 
 
-# ---- thin callers: inputs are CPU tensors, outputs are what the reference operator returns -------
+# ---- thin callers: inputs are CPU tensors (or device tensors when native), outputs are what the
+# ---- reference operator returns
 
 def rmsnorm(x, w, eps, dy):
     """-> y, dx, dw of reference ``triton_rmsnorm`` (core/rmsnorm.py:90)."""

@@ -70,3 +70,26 @@ def cuda():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda", 0)
+
+
+def assert_close_device(actual, expected, rel, what="", rows_per_block=2048):
+    """`assert_close` for tensors too large to bring to the host: the same bound
+    |a - b| <= rel * (|b| + mean|b|), evaluated on the device block of rows by block of rows."""
+    assert actual.shape == expected.shape, f"{what}: shape {tuple(actual.shape)} vs {tuple(expected.shape)}"
+    a2 = actual.detach().reshape(-1, actual.shape[-1])
+    b2 = expected.detach().reshape(-1, expected.shape[-1])
+    n = a2.shape[0]
+    total = torch.zeros((), dtype=torch.float64, device=b2.device)
+    for i in range(0, n, rows_per_block):
+        total += b2[i:i + rows_per_block].float().abs().sum(dtype=torch.float64)
+    scale = (total / max(1, b2.numel())).float()
+    bad = 0
+    worst = 0.0
+    for i in range(0, n, rows_per_block):
+        a = a2[i:i + rows_per_block].float(); b = b2[i:i + rows_per_block].float()
+        assert torch.isfinite(a).all(), f"{what}: non-finite values"
+        err = (a - b).abs()
+        tol = rel * (b.abs() + scale) + 1e-30
+        bad += int((err > tol).sum())
+        worst = max(worst, float((err / tol).max()))
+    assert bad == 0, f"{what}: {bad}/{a2.numel()} elements out of tolerance rel={rel}; worst error/tolerance {worst:.3g}"

@@ -2,7 +2,7 @@
 
     TRITON_INTERPRET=1 python tests/golden/make_golden.py [file.pt ...]
 
-Needs a reference checkout (located by ``oracle/ref_loader.py``, ``MDY_REFERENCE_ROOT``).  Each case stores its
+Needs the reference's kernel files staged by ``python -m oracle.make_ref``.  Each case stores its
 seeded inputs and the outputs / gradients the reference operator produced for them when run on CPU
 under Triton's interpreter.  The files are small on purpose; they travel with the repository to
 machines that have no reference checkout.
@@ -161,7 +161,7 @@ def case_maxmin():
 
 def main():
     if not R.available():
-        raise SystemExit(f"no reference checkout at {R.REFERENCE_ROOT}")
+        raise SystemExit("no staged reference kernels: run python -m oracle.make_ref first")
     only = set(sys.argv[1:])  # optional: file names to (re)generate; default all
     for fname, fn in {"rmsnorm.pt": case_rmsnorm, "add_rmsnorm.pt": case_add_rmsnorm, "rope.pt": case_rope,
                       "swiglu.pt": case_swiglu, "cross_entropy.pt": case_ce, "maxmin.pt": case_maxmin}.items():

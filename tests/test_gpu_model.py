@@ -6,6 +6,7 @@ import functools
 import json
 import subprocess
 import sys
+import tempfile
 from pathlib import Path
 
 import pytest
@@ -56,6 +57,7 @@ out = model(input_ids=ids, labels=labels)
 hook.remove()
 out.loss.backward()
 res = {{"loss": float(out.loss), "logits_shape": list(out.logits.shape), "layer_output_type": seen[0]}}
+samples = {{}}
 params = {{k.replace("model.language_model.", "model."): v for k, v in model.named_parameters()}}
 for name in ("model.embed_tokens.weight", "model.layers.0.input_layernorm.weight", "model.layers.1.post_attention_layernorm.weight",
              "model.layers.0.self_attn.q_proj.weight", "model.layers.0.self_attn.qkv_proj.weight", "model.layers.1.mlp.gate_proj.weight",
@@ -64,6 +66,8 @@ for name in ("model.embed_tokens.weight", "model.layers.0.input_layernorm.weight
         continue
     p = params[name]
     res[name] = [float(p.grad.float().norm()), float(p.grad.float().flatten()[:64].sum())]
+    flat = p.grad.float().flatten()
+    samples[name] = flat[::max(1, flat.numel() // 4096)][:4096].cpu()   # a fixed strided sample, compared elementwise
 with torch.no_grad():
     res["eval_loss"] = float(model(input_ids=ids, labels=labels).loss)
     gen = model.generate(ids[:1, :8], max_new_tokens=4, do_sample=False)
@@ -77,6 +81,7 @@ out = model(input_ids=ids, labels=labels)
 out.loss.backward()
 res["ckpt_loss"] = float(out.loss)
 res["ckpt_grad"] = [float(params["lm_head.weight"].grad.float().norm()), float(params["model.embed_tokens.weight"].grad.float().norm())]
+torch.save(samples, sys.argv[4])
 print("RESULT " + json.dumps(res))
 """
 
@@ -84,11 +89,15 @@ print("RESULT " + json.dumps(res))
 @functools.lru_cache(maxsize=None)
 def _run(family, patched, dtype):
     """patched: False = stock model, True = patched, 2 = patched with residual fusion switched on."""
-    r = subprocess.run([sys.executable, "-c", CHILD.format(root=str(ROOT)), family, str(int(patched)), dtype],
-                       capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0, r.stderr[-3000:]
-    line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
-    return json.loads(line[7:])
+    with tempfile.TemporaryDirectory() as tmp:
+        grads = str(Path(tmp) / "grads.pt")
+        r = subprocess.run([sys.executable, "-c", CHILD.format(root=str(ROOT)), family, str(int(patched)), dtype, grads],
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-3000:]
+        line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
+        res = json.loads(line[7:])
+        res["grad_samples"] = torch.load(grads)
+    return res
 
 
 @pytest.mark.parametrize("family", ["llama", "qwen2", "mistral", "phi3", "qwen2_vl", "glm"])
@@ -103,10 +112,25 @@ def test_patched_model_matches_stock_model_fp32(family):
     assert b["layer_output_type"] == "Tensor"
 
 
+def _same_gradient_samples(a, b, rel, l2):
+    """Elementwise on a fixed 4096-element strided sample of each parameter's gradient:
+    |patched - stock| <= rel * (|stock| + rms(stock)), and the sample's relative L2 distance <= l2."""
+    assert a["grad_samples"].keys() == b["grad_samples"].keys() and len(a["grad_samples"]) >= 7
+    for k, ga in a["grad_samples"].items():
+        gb = b["grad_samples"][k]
+        assert ga.shape == gb.shape and torch.isfinite(gb).all()
+        rms = ga.pow(2).mean().sqrt()
+        err = (ga - gb).abs()
+        worst = float((err / (rel * (ga.abs() + rms) + 1e-30)).max())
+        rel_l2 = float((ga - gb).norm() / ga.norm().clamp_min(1e-30))
+        assert worst <= 1.0 and rel_l2 <= l2, f"{k}: worst error/tolerance {worst:.3g} (rel {rel}), relative L2 {rel_l2:.3g} (limit {l2})"
+
+
 def _same_gradients(a, b, rel=2e-3):
     for k, v in a.items():
         if isinstance(v, list) and len(v) == 2 and k not in ("logits_shape",):
             assert abs(v[0] - b[k][0]) <= rel * max(1e-6, abs(v[0])), (k, v, b[k])
+    _same_gradient_samples(a, b, 1e-4, 1e-4)
     assert abs(a["ckpt_loss"] - b["ckpt_loss"]) <= 1e-4 * max(1.0, abs(a["ckpt_loss"]))
     assert len(a["hidden_norms"]) == len(b["hidden_norms"])
     for x, y in zip(a["hidden_norms"], b["hidden_norms"]):
@@ -126,10 +150,30 @@ def test_residual_fusion_matches_stock_model_fp32(family):
     _same_gradients(a, b)
 
 
-def test_patched_model_matches_stock_model_bf16():
-    a = _run("llama", False, "bfloat16")
-    b = _run("llama", True, "bfloat16")
+@pytest.mark.parametrize("family", ["llama", "qwen2", "mistral", "phi3", "qwen2_vl", "glm"])
+def test_patched_model_matches_stock_model_bf16(family):
+    """bfloat16 weights and activations.  The stock modules round intermediates to bfloat16 that the fused
+    kernels keep in float32 (the normalised row before the weight, silu(gate) before the product, float32
+    logits in the loss), so the two gradients differ by rounding noise: bounded elementwise on the strided
+    sample by 1e-2 relative with a floor of the sample's rms, after taking out what the stock model's own
+    bfloat16 rounding contributes, measured against its float32 run."""
+    ref32 = _run(family, False, "float32")
+    a = _run(family, False, "bfloat16")
+    b = _run(family, True, "bfloat16")
     assert abs(a["loss"] - b["loss"]) <= 2e-2 * max(1.0, abs(a["loss"]))
     for k, v in a.items():
         if isinstance(v, list) and len(v) == 2 and k != "logits_shape":
             assert abs(v[0] - b[k][0]) <= 5e-2 * max(1e-6, abs(v[0])), (k, v, b[k])
+    report = {}
+    for k, g32 in ref32["grad_samples"].items():
+        ga, gb = a["grad_samples"][k], b["grad_samples"][k]
+        rms = g32.pow(2).mean().sqrt()
+        stock_noise = float(((ga - g32).abs() / (g32.abs() + rms)).max())      # stock bf16 against stock float32
+        ours_noise = float(((gb - g32).abs() / (g32.abs() + rms)).max())       # patched bf16 against stock float32
+        report[k] = (round(stock_noise, 4), round(ours_noise, 4))
+        # The patched model is no further from the float32 gradient than the stock bfloat16 model is, up to
+        # 1e-2: in relative L2 distance over the sample, and (the maximum of a noise being itself noisy, within
+        # a factor of two) in the worst element.
+        l2_stock = float((ga - g32).norm() / g32.norm()); l2_ours = float((gb - g32).norm() / g32.norm())
+        assert l2_ours <= l2_stock + 1e-2, (k, l2_stock, l2_ours, report)
+        assert ours_noise <= 2 * stock_noise + 1e-2, (k, report)

@@ -433,6 +433,44 @@ def test_ce_upstream_gradient_scaling(fused_impl):
     assert_close(x.grad, E.ce_grad(lg, lb, lse, torch.tensor(0.25 / 32)), 1e-2)
 
 
+def test_ce_float16_with_a_loss_scaler_keeps_small_gradients():
+    """float16 logits under a GradScaler: loss * 65536 is what gets differentiated.  The gradient of a rare
+    token, (softmax - onehot) / n_items, is below float16's smallest subnormal, but times the scale it is
+    representable: it must arrive, not be flushed to zero before the scale is applied."""
+    gen = g(11)
+    m, v, scale = 64, 32000, 65536.0
+    lg = (torch.randn(m, v, generator=gen) * 4).to(torch.float16); lb = torch.randint(0, v, (m,), generator=gen)
+    x = leaf(lg)
+    (triton_entropy_loss(x, lb.to(DEV)) * scale).backward()
+    _, lse = E.ce_rows(lg, lb)
+    want = E.ce_grad(lg, lb, lse, torch.tensor(scale / m))
+    assert_close(x.grad, want, 1e-2, "scaled float16 dlogits", 2.0 ** -24)
+    unscaled = E.ce_grad(lg, lb, lse, torch.tensor(1.0 / m)).abs()
+    lost = (unscaled < 2.0 ** -25) & (want.abs() >= 2.0 ** -14)   # flushed without the scale, normal with it
+    assert lost.any()
+    assert (x.grad.cpu()[lost] != 0).all()
+
+
+def test_ce_one_pass_gradient_is_handed_out_once():
+    """The one-pass path keeps no logits, only the gradient it wrote: a second backward through the same loss
+    would rescale the tensor the first one returned, so it raises instead; the per-row function, which the
+    reference also offers, can be walked twice."""
+    gen = g(12)
+    lg = (torch.randn(16, 2048, generator=gen) * 2).to(torch.bfloat16); lb = torch.randint(0, 2048, (16,), generator=gen).to(DEV)
+    x = leaf(lg)
+    loss = triton_entropy_loss(x, lb)
+    (loss * 0.5).backward(retain_graph=True)
+    first = x.grad.clone()
+    with pytest.raises(RuntimeError, match="once"):
+        (loss * 0.5).backward()
+    assert torch.equal(x.grad, first)
+    x = leaf(lg)
+    losses = _FastCrossEntropyLoss.apply(x, lb, False)
+    losses.sum().backward(retain_graph=True); g1 = x.grad.clone(); x.grad = None
+    losses.sum().backward()
+    assert torch.equal(x.grad, g1)
+
+
 def test_ce_out_of_range_label_and_neg_inf_logits():
     lg = torch.randn(4, 64) * 2
     lg[1, 10:20] = float("-inf")
@@ -477,6 +515,89 @@ def test_ce_properties_full_size(fused_impl):
     lo, lse_o = E.ce_rows(lg[sl].cpu(), lb[sl].cpu())
     assert torch.allclose(l2[sl].cpu(), lo, rtol=LOSS_TOL, atol=LOSS_TOL)
     assert_close(d[sl], E.ce_grad(lg[sl].cpu(), lb[sl].cpu(), lse_o, torch.tensor(1.0 / n)), 1e-2)
+
+
+def test_ce_bounded_wait_runs_out_sets_the_flag_and_poisons_the_loss():
+    """Failure detection of the cluster kernel, without faulting anything: a test hook shortens the bound of
+    its mbarrier waits to about a millisecond and leaves one chunk of one row unrequested, so the wait for
+    it runs out.  The launch must still return, the device must stay usable, the flag must be raised, the
+    affected row's loss must be NaN (never a finite wrong number), and the next launch must be correct."""
+    import time
+    lib = _C.lib()
+    gen = g(21)
+    m, v = 8, 128256
+    lg = (torch.randn(m, v, generator=gen) * 3).to(torch.bfloat16); lb = torch.randint(0, v, (m,), generator=gen)
+    lo, lse_o = E.ce_rows(lg, lb)
+    x, labels = lg.to(DEV), lb.to(DEV)
+    inv = torch.full((1,), 1.0 / m, device=DEV)
+
+    def run():
+        dl = torch.empty_like(x); losses = torch.empty(m, device=DEV); lse = torch.empty(m, device=DEV)
+        rc = lib.mdy_ce_fused(x.data_ptr(), dl.data_ptr(), labels.data_ptr(), losses.data_ptr(), lse.data_ptr(),
+                              inv.data_ptr(), 1.0, m, v, v, _C.MDY_BF16, torch.cuda.current_stream().cuda_stream)
+        return rc, dl, losses
+
+    torch.cuda.synchronize()
+    assert lib.mdy_last_device_error(1) == 0
+    _C.set_tunable(_C.TUNE_CE_WAIT_TEST, 1)
+    try:
+        t0 = time.perf_counter()
+        rc, _, losses = run()
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+    finally:
+        _C.set_tunable(_C.TUNE_CE_WAIT_TEST, 0)
+    assert rc == 0
+    assert elapsed < 1.0, f"the kernel took {elapsed:.2f} s to give up"
+    assert lib.mdy_last_device_error(1) == 1, "the expired wait was not flagged"
+    assert lib.mdy_last_device_error(0) == 0, "the flag was not cleared"
+    losses = losses.cpu()
+    assert torch.isnan(losses[0]), "the row whose data never arrived must not get a finite loss"
+    assert torch.allclose(losses[1:], lo[1:], rtol=LOSS_TOL, atol=LOSS_TOL)
+    # the context is intact: the same launch without the hook is correct
+    rc, dl, losses = run()
+    torch.cuda.synchronize()
+    assert rc == 0 and lib.mdy_last_device_error(1) == 0
+    assert torch.allclose(losses.cpu(), lo, rtol=LOSS_TOL, atol=LOSS_TOL)
+    assert_close(dl, E.ce_grad(lg, lb, lse_o, torch.tensor(1.0 / m)), 1e-2, "dlogits after the expired wait")
+
+
+def test_config1_full_size_against_the_cpu_oracle():
+    """The Qwen2-0.5B-shaped configuration in full (4 x 1024 tokens, seed 0): float32 on the CPU oracle, the
+    bfloat16 cast of the same draw on the GPU.  RMSNorm [4096, 896], RoPE 14 q / 2 kv heads x 64, SwiGLU
+    [4096, 4864], cross-entropy [4096, 151936] with 5 % of the labels ignored."""
+    gen = g(0)
+    dt = torch.bfloat16
+    M, H, F, V, B, L, QH, KH, D = 4096, 896, 4864, 151936, 4, 1024, 14, 2, 64
+    x = torch.randn(M, H, generator=gen); w = 1 + 0.02 * torch.randn(H, generator=gen); dy = torch.randn(M, H, generator=gen)
+    y, dx, dw = run_rmsnorm(x.to(dt), w.to(dt), 1e-6, dy.to(dt))
+    yo, _ = E.rmsnorm_fwd(x.to(dt), w.to(dt), 1e-6); dxo, dwo = E.rmsnorm_bwd(dy.to(dt), x.to(dt), w.to(dt), 1e-6)
+    assert_close(y, yo, 1e-2, "rmsnorm y"); assert_close(dx, dxo, 1e-2, "rmsnorm dx"); assert_close(dw, dwo, 1e-2, "rmsnorm dw")
+    q = torch.randn(B, L, QH, D, generator=gen).to(dt); k = torch.randn(B, L, KH, D, generator=gen).to(dt)
+    dq = torch.randn(B, QH, L, D, generator=gen).to(dt); dk = torch.randn(B, KH, L, D, generator=gen).to(dt)
+    cos, sin = E.rope_cos_sin(torch.arange(L)[None], D, 1e6, dt)
+    qs, ks = leaf(q), leaf(k)
+    qe, ke = core.fused_apply_rope((qs * 1.0).transpose(1, 2), (ks * 1.0).transpose(1, 2), cos.to(DEV), sin.to(DEV))
+    qv, kv = qe.detach().clone(), ke.detach().clone()
+    torch.autograd.backward([qe, ke], [dq.to(DEV), dk.to(DEV)])
+    qo, ko = E.rope_fwd(q.transpose(1, 2), k.transpose(1, 2), cos, sin); gq, gk = E.rope_bwd(dq, dk, cos, sin)
+    assert_close(qv, qo, 1e-2, "rope q"); assert_close(kv, ko, 1e-2, "rope k")
+    assert_close(qs.grad.transpose(1, 2), gq, 1e-2, "rope dq"); assert_close(ks.grad.transpose(1, 2), gk, 1e-2, "rope dk")
+    up = torch.randn(M, F, generator=gen).to(dt); gate = torch.randn(M, F, generator=gen).to(dt); sdy = torch.randn(M, F, generator=gen).to(dt)
+    ug, gg = leaf(up), leaf(gate)
+    sy = core.triton_fused_up_gate_silu(ug, gg); sy.backward(sdy.to(DEV))
+    du, dg = E.swiglu_bwd(sdy, up, gate)
+    assert_close(sy, E.swiglu_fwd(up, gate), 1e-2, "swiglu y"); assert_close(ug.grad, du, 1e-2, "swiglu dup"); assert_close(gg.grad, dg, 1e-2, "swiglu dgate")
+    del ug, gg, sy, du, dg
+    lg = (torch.randn(M, V, generator=gen) * 2).to(dt); lb = torch.randint(0, V, (M,), generator=gen)
+    lb[torch.rand(M, generator=gen) < 0.05] = -100
+    xg = leaf(lg)
+    loss = triton_entropy_loss(xg.view(B, L, V), lb.view(B, L).to(DEV)); loss.backward()
+    lo, lse = E.ce_rows(lg, lb)
+    n = int((lb != -100).sum())
+    loss_close(loss, lo.sum() / n)
+    want = E.ce_grad(lg, lb, lse, torch.tensor(1.0 / n))
+    assert_close(xg.grad, want, 1e-2, "cross-entropy dlogits")
 
 
 def test_ce_cluster_launch_geometry():

@@ -73,6 +73,16 @@ def _gloo_worker(rank, world, port, fail_rank, out):
         shard2 = lg[:, rank * v:(rank + 1) * v].contiguous().requires_grad_(True)
         loss = vocab_parallel_entropy_loss(shard2, lb)
         ok = ok and abs(float(loss) - float(E.ce_scalar(lg, lb))) < 1e-5
+        # the Megatron-facing adapter (reference triton_kernels/megatron_patchs/cross_entropy_losss.py:139-140):
+        # same losses, and the gradient lands in the logits' own storage
+        from mdy_triton_b200.core.megatron import vocab_parallel_cross_entropy as megatron_ce
+        leaf = lg[:, rank * v:(rank + 1) * v].contiguous().requires_grad_(True)
+        work = leaf * 1.0                       # the non-leaf tensor a model would hand to the loss
+        m_losses = megatron_ce(work.view(4, 12, v), lb.view(4, 12))
+        m_losses.view(-1).backward(dl)
+        ok = (ok and torch.allclose(m_losses.view(-1), full_losses, atol=1e-5)
+              and torch.allclose(leaf.grad, full_grad[:, rank * v:(rank + 1) * v], atol=1e-6)
+              and torch.equal(work.detach(), leaf.grad))   # in place: the logits now hold their gradient
         out[rank] = "ok" if ok else "mismatch"
     except Exception as e:  # noqa: BLE001
         out[rank] = f"error: {type(e).__name__}"
