@@ -476,6 +476,7 @@ def run_llama1b(dev, dist, world, steps, warmup, patched=True, micro_batch=4, se
                       num_key_value_heads=8, head_dim=64, vocab_size=128256, rms_norm_eps=1e-5, rope_theta=500000.0,
                       max_position_embeddings=seq, tie_word_embeddings=False, attn_implementation="sdpa")
     torch.manual_seed(1234)
+    torch.cuda.reset_peak_memory_stats(dev)
     with torch.device(dev):
         model = LlamaForCausalLM(cfg).to(torch.bfloat16)
     model.train()
@@ -557,10 +558,14 @@ def _vpce_shard(dev, M, vs, sigma, r):
 def run_vpce(dev, dist, world, rank, steps, warmup, check=True):
     """Vocab-parallel sweep: 16384 tokens, vocab in {32000, 128256, 151936, 256000} sharded over the ranks,
     logits N(0, sigma^2) with sigma in {1, 4}, 5 % of the labels -100, bf16, gradient written in place.
-    Per step and rank: local sweep (mdy_ce_fwd, split mode) -> one all_gather of [2, M] float32 ->
-    mdy_ce_vp_combine -> local gradient sweep (mdy_ce_bwd).  The collective is inside the timed region.
-    With `check`, every case's loss is compared on the device with the loss the one-pass kernel gives on the
-    full vocabulary (all shards side by side on this GPU): they must agree to 1e-4."""
+    Per step and rank ONE kernel (mdy_ce_vp_fused): statistics sweep, exchange of the per-row records by
+    stores into every rank's exchange buffer (peer memory over NVLink), gradient sweep from the slices still
+    in shared memory; the exchange is inside the kernel, hence inside the timed region.  Shapes the kernel
+    has no geometry for take the three-step path (mdy_ce_fwd in split mode -> one all_gather of [2, M]
+    float32 -> mdy_ce_vp_combine -> mdy_ce_bwd), the collective again inside the timed region; each case
+    says which path it took.  With `check`, every case's loss and this rank's gradient columns are compared
+    on the device with what the one-pass kernel gives on the full vocabulary (all shards side by side on
+    this GPU): 1e-4 on the loss, 1e-2 relative on the gradient."""
     from mdy_triton_b200.core import vocab_parallel as vp
     import mdy_triton.core as core
     M = VPCE_TOKENS
@@ -579,8 +584,15 @@ def run_vpce(dev, dist, world, rank, steps, warmup, check=True):
             stats = torch.empty(2, M, dtype=torch.float32, device=dev)
             gathered = torch.empty(world, 2, M, dtype=torch.float32, device=dev)
             work = torch.empty_like(shard)
+            inv_m = torch.full((1,), 1.0 / M, device=dev)
+            try:
+                exchange = vp.PeerExchange(M, vs, torch.bfloat16, dev)
+            except ValueError:
+                exchange = None
 
             def timed():
+                if exchange is not None:
+                    return vp.fused_loss_and_grad(work, labels, work, inv_m, exchange)[0]
                 vp._local_forward(work, labels, vs * rank, stats)
                 if dist is not None:
                     dist.all_gather_into_tensor(gathered.view(-1), stats.view(-1))
@@ -606,7 +618,8 @@ def run_vpce(dev, dist, world, rank, steps, warmup, check=True):
                 dist.all_reduce(tt, op=dist.ReduceOp.MAX)
                 t = float(tt[0])
             loss = float(losses.sum() / n_valid)
-            case = {"vocab": vs * world, "sigma": sigma, "ms": t}
+            case = {"vocab": vs * world, "sigma": sigma, "ms": t,
+                    "path": "one kernel, records stored into peer memory" if exchange is not None else "sweep, all-gather, sweep"}
             alg = M * vs * 2 * (2 - f_ign) * world
             case.update({"algorithmic_GBps": alg / t / 1e6, "loss": loss})
             del work
@@ -620,14 +633,17 @@ def run_vpce(dev, dist, world, rank, steps, warmup, check=True):
                 ref.backward()
                 # and this rank's gradient against the matching columns of the full-vocabulary gradient
                 work2 = shard.clone()
-                vp._local_forward(work2, labels, vs * rank, stats)
-                if dist is not None:
-                    dist.all_gather_into_tensor(gathered.view(-1), stats.view(-1))
+                if exchange is not None:
+                    vp.fused_loss_and_grad(work2, labels, work2, (1.0 / n_valid.float()).reshape(1), exchange)
                 else:
-                    gathered[0].copy_(stats)
-                _, lse = vp._combine(gathered, labels)
-                dn = torch.full((M,), 1.0, device=dev) / n_valid
-                vp._local_backward(dn, work2, labels, lse, work2, vs * rank)
+                    vp._local_forward(work2, labels, vs * rank, stats)
+                    if dist is not None:
+                        dist.all_gather_into_tensor(gathered.view(-1), stats.view(-1))
+                    else:
+                        gathered[0].copy_(stats)
+                    _, lse = vp._combine(gathered, labels)
+                    dn = torch.full((M,), 1.0, device=dev) / n_valid
+                    vp._local_backward(dn, work2, labels, lse, work2, vs * rank)
                 want = full.grad[:, rank * vs:(rank + 1) * vs].float()
                 err = (work2.float() - want).abs()
                 grad_ok = bool((err <= 1e-2 * (want.abs() + want.abs().mean())).all())
@@ -642,9 +658,17 @@ def run_vpce(dev, dist, world, rank, steps, warmup, check=True):
                     parity = f"MISMATCH at vocab {V} sigma {sigma}: {loss} vs {float(ref)}, gradient ok: {grad_ok}"
                 del full, ref
             cases.append(case)
+            if exchange is not None:
+                exchange.close()
             del shard
             torch.cuda.empty_cache()
     return cases, parity
+
+
+def _device_error_flag():
+    """0 unless a bounded device-side wait expired during the run (mdy_last_device_error)."""
+    from mdy_triton_b200 import _C
+    return int(_C.lib().mdy_last_device_error(1))
 
 
 def vpce_summary(cases, parity, world, peak):
@@ -656,7 +680,7 @@ def vpce_summary(cases, parity, world, peak):
             "parity": parity, "parity_check": "each case: loss and this rank's gradient columns against the one-pass kernel on "
             "the full vocabulary on one GPU (1e-4 on the loss, 1e-2 relative on the gradient)",
             "workload": "16384 tokens, vocab sharded over the GPUs, per-row statistics exchanged inside the timed region, "
-                        "gradient in place", "cases": cases}
+                        "gradient in place", "device_error_flag": _device_error_flag(), "cases": cases}
 
 
 # -------------------------------------------------------------------------------- one operator at a time

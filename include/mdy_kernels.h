@@ -5,8 +5,9 @@
  * (cited per function as file:line within the reference project).
  *
  * Conventions
- *   - All pointers are DEVICE pointers owned by the caller.  The library allocates nothing and keeps
- *     no state apart from a per-process cached SM count, a launch counter and integer tunables.
+ *   - All pointers are DEVICE pointers owned by the caller.  The operator entry points allocate nothing
+ *     and keep no state apart from a per-process cached SM count, a launch counter and integer tunables
+ *     (the one exception is the set-up call mdy_peer_buffer_create, which exists to allocate).
  *   - Work is enqueued asynchronously on `stream` (a cudaStream_t passed as void*; NULL = legacy
  *     default stream).  No entry point synchronises the host.
  *   - `dtype` is one of MDY_F32 / MDY_F16 / MDY_BF16 and names the element type of every tensor
@@ -232,6 +233,56 @@ int mdy_rowwise_extreme(const void* x, void* values, int64_t* indices, int64_t M
  * core/cross_entyopy_loss.py:109-117 (all_gather + all_reduce + logsumexp + masked_fill). */
 int mdy_ce_vp_combine(const float* gathered, const int64_t* labels, float* losses, float* lse,
                       int64_t tp, int64_t M, void* stream);
+
+/* ---- vocab-parallel cross-entropy in one kernel per GPU ------------------------------------- */
+
+/* The whole tensor-parallel loss of triton_kernels/cross_entropy/test_ce.py:110-166 (local statistics,
+ * the all-gather / all-reduce of core/cross_entyopy_loss.py:109-117, the gradient kernel launched at
+ * :133-141) as ONE launch per GPU: each CTA stages row slices of its rank's shard in shared memory,
+ * publishes (local lse, -logit[label]) for a row by storing a 16-byte record straight into every rank's
+ * exchange buffer (peer memory, over NVLink), and a few rows later polls its own buffer for the records
+ * of all ranks, forms the global lse and the loss, and writes (softmax - onehot) * g from the slice it
+ * still holds.  The shard is read once and written once; there is no NCCL call.
+ *
+ *   logits / dlogits / losses / lse   host arrays of n_local_ranks DEVICE pointers: the shard T [M,
+ *              shard_cols] (row_stride elements apart), its gradient (may be the same buffer), and the
+ *              float [M] outputs (global lse and loss, identical on every rank) of ranks first_rank ..
+ *              first_rank + n_local_ranks - 1.  In production n_local_ranks is 1 (one process per GPU);
+ *              a larger value runs several ranks' shards as one launch on one GPU, which is how the
+ *              exchange is exercised where there are fewer GPUs than ranks.
+ *   exchange   host array of tp DEVICE pointers, indexed by rank: every rank's exchange buffer as this
+ *              process can address it (its own from mdy_peer_buffer_create, the peers' from
+ *              mdy_peer_buffer_open), each of mdy_ce_vp_exchange_bytes(exchange_rows, ...) bytes,
+ *              zero-filled once.  The same buffers serve every call.
+ *   labels     int64 [M], global vocabulary ids, identical on every rank; MDY_IGNORE_INDEX rows get zero
+ *              gradient and loss and take no part in the exchange.
+ *   g          grad_scale_host * (*grad_scale_dev if given): the upstream gradient of every row.
+ *   epoch      a counter the caller advances by one per call, from 1, in step on all ranks (0 is not
+ *              allowed): records of an older call are ignored.
+ * All ranks must call it with the same M, shard_cols, tp, exchange_rows and epoch, each on its own GPU at
+ * about the same time: a CTA waits, bounded to a few seconds, for the peers' records.  If a wait runs out
+ * the affected rows get NaN loss and lse and mdy_last_device_error reports 2; nothing hangs.  The kernels of
+ * one call on the participating GPUs must all be able to run at once: do not keep the SMs of a rank busy
+ * with a kernel that itself waits for this one.
+ * Returns MDY_ERR_UNSUPPORTED (launching nothing) for shards it has no geometry for (columns not a
+ * multiple of the 16-byte vector, more than 32 participants per row, unaligned buffers): callers then use
+ * mdy_ce_fwd -> all-gather -> mdy_ce_vp_combine -> mdy_ce_bwd. */
+int mdy_ce_vp_fused(const void* const* logits, void* const* dlogits, float* const* losses, float* const* lse,
+                    void* const* exchange, const int64_t* labels, const float* grad_scale_dev,
+                    float grad_scale_host, int64_t M, int64_t shard_cols, int64_t row_stride, int tp,
+                    int first_rank, int n_local_ranks, int64_t exchange_rows, uint32_t epoch, int dtype,
+                    void* stream);
+/* Bytes of one rank's exchange buffer for up to max_rows rows (negative: MDY_ERR_*). */
+int64_t mdy_ce_vp_exchange_bytes(int64_t max_rows, int64_t shard_cols, int tp, int dtype);
+
+/* Set-up of memory that peers write into (not on the hot path; the reference has no counterpart: it
+ * leaves the exchange to NCCL).  create: cudaMalloc + zero fill on the current device, and the 64-byte
+ * CUDA IPC handle to pass to the other processes; open: map a peer's buffer from its handle (peer
+ * access is enabled as needed); close / destroy undo them. */
+int mdy_peer_buffer_create(int64_t bytes, void** ptr, void* ipc_handle_64_bytes);
+int mdy_peer_buffer_open(const void* ipc_handle_64_bytes, void** ptr);
+int mdy_peer_buffer_close(void* ptr);
+int mdy_peer_buffer_destroy(void* ptr);
 
 #ifdef __cplusplus
 }

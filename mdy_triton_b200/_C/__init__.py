@@ -38,6 +38,10 @@ TUNE_NORM_POW2_GROUPS = 16
 TUNE_NORM_FWD_GROUP = 17
 TUNE_NORM_BWD_GROUP = 18
 TUNE_NORM_FWD_THREADS = 19
+TUNE_NORM_IMPL = 20
+TUNE_CE_VP_CTAS_PER_SM = 21
+TUNE_CE_VP_SLOTS = 22
+TUNE_NORM_TEAM = 24
 
 _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 
@@ -66,6 +70,12 @@ SIGNATURES = {
     "mdy_ce_fused": (_I, [_P, _P, _P, _P, _P, _P, _F, _L, _L, _L, _I, _P]),
     "mdy_scale_inplace": (_I, [_P, _L, _P, _I, _P]),
     "mdy_ce_vp_combine": (_I, [_P, _P, _P, _P, _L, _L, _P]),
+    "mdy_ce_vp_fused": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _L, _L, _L, _I, _I, _I, _L, ctypes.c_uint32, _I, _P]),
+    "mdy_ce_vp_exchange_bytes": (_L, [_L, _L, _I, _I]),
+    "mdy_peer_buffer_create": (_I, [_L, _P, _P]),
+    "mdy_peer_buffer_open": (_I, [_P, _P]),
+    "mdy_peer_buffer_close": (_I, [_P]),
+    "mdy_peer_buffer_destroy": (_I, [_P]),
 }
 
 _lib = None

@@ -52,11 +52,17 @@ class _FusedApplyRope(torch.autograd.Function):
             raise ValueError("q and k disagree on batch, seq or head_dim")
         if cos.dim() == 2:
             cos, sin = cos.unsqueeze(0), sin.unsqueeze(0)
-        if cos.shape[-2:] != (l, d) or cos.shape != sin.shape or cos.shape[0] not in (1, b):
-            raise ValueError(f"cos/sin must be [{b} or 1, {l}, {d}], got {tuple(cos.shape)}")
+        rd = cos.shape[-1]
+        if (cos.shape[-2] != l or rd > d or rd % 2 or rd == 0 or cos.shape != sin.shape
+                or cos.shape[0] not in (1, b)):
+            raise ValueError(f"cos/sin must be [{b} or 1, {l}, rotary_dim <= {d}], got {tuple(cos.shape)}")
         cos = cos.to(q.dtype).contiguous()
         sin = sin.to(q.dtype).contiguous()
-        _launch(q, q, k, k, cos, sin, backward=False)
+        # Partial rotary embedding (HuggingFace Phi3 / GLM with partial_rotary_factor < 1: rotary_dim =
+        # cos.shape[-1]): only the first rotary_dim columns of every head are rotated, the rest pass through.
+        # The kernel takes the head stride separately from the rotated width, so it runs on a view.
+        qv, kv = (q, k) if rd == d else (q[..., :rd], k[..., :rd])
+        _launch(qv, qv, kv, kv, cos, sin, backward=False)
         ctx.save_for_backward(cos, sin)
         return q, k
 
@@ -75,7 +81,13 @@ class _FusedApplyRope(torch.autograd.Function):
         kh = dk.shape[1]
         dq_out = torch.empty((b, l, qh, d), dtype=dq.dtype, device=dq.device).transpose(1, 2)
         dk_out = torch.empty((b, l, kh, d), dtype=dk.dtype, device=dk.device).transpose(1, 2)
-        _launch(dq, dq_out, dk, dk_out, cos, sin, backward=True)
+        rd = cos.shape[-1]
+        if rd == d:
+            _launch(dq, dq_out, dk, dk_out, cos, sin, backward=True)
+        else:
+            _launch(dq[..., :rd], dq_out[..., :rd], dk[..., :rd], dk_out[..., :rd], cos, sin, backward=True)
+            dq_out[..., rd:].copy_(dq[..., rd:])
+            dk_out[..., rd:].copy_(dk[..., rd:])
         return dq_out, dk_out, None, None
 
 

@@ -7,6 +7,12 @@ local sweep -> exchange of per-row statistics -> global lse and loss -> local gr
 global lse.  The exchange is ONE ``all_gather_into_tensor`` of a float32 ``[2, M]`` tensor per rank
 (local lse, and ``-logit[label]`` on the rank that owns the label) on the given process group; the
 reference uses an all-gather plus an all-reduce on the default group.  Backward needs no collective.
+
+``vocab_parallel_entropy_loss`` (the scalar loss, whose per-row upstream gradient ``1 / n_items`` is known
+before the kernel starts) can go further when it is given a :class:`PeerExchange`: ONE kernel per GPU
+computes the statistics, exchanges them by storing straight into the peers' memory over NVLink, and writes
+the gradient from the row slices it still holds in shared memory (``mdy_ce_vp_fused``) — the shard is read
+once and written once and there is no NCCL call on the path.
 """
 from __future__ import annotations
 
@@ -72,14 +78,133 @@ class _VocabParallelCrossEntropy(torch.autograd.Function):
         return dlogits.view(ctx.input_shape), None, None, None
 
 
+class PeerExchange:
+    """Exchange buffers for the one-kernel path: one buffer per rank of ``group``, allocated by the
+    library (a peer has to be able to map it), made known to the other ranks through CUDA IPC handles that
+    travel over ``group`` once, here.  ``max_rows`` bounds the rows of a call; ``shard_cols`` and ``dtype``
+    fix the geometry.  Create it once, outside the training loop (it allocates and synchronises), and pass
+    it to :func:`vocab_parallel_entropy_loss`; every rank must then make the same calls in the same order.
+    With ``group=None`` and no initialised process group it serves a single rank."""
+
+    def __init__(self, max_rows, shard_cols, dtype, device, group=None):
+        import ctypes
+        self.group = group
+        self.device = torch.device(device)
+        self.tp = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.max_rows, self.shard_cols, self.dtype = int(max_rows), int(shard_cols), dtype
+        lib = _C.lib()
+        nbytes = lib.mdy_ce_vp_exchange_bytes(self.max_rows, self.shard_cols, self.tp, _C.DTYPE_CODE[dtype])
+        if nbytes < 0:
+            raise ValueError(f"no one-kernel geometry for shards of {shard_cols} columns over {self.tp} ranks: "
+                             f"{_C.status_string(nbytes)}")
+        self.epoch = 0
+        self._own = ctypes.c_void_p()
+        self._opened = []
+        handle = ctypes.create_string_buffer(64)
+        with torch.cuda.device(self.device):
+            _C.check(lib.mdy_peer_buffer_create(nbytes, ctypes.byref(self._own), handle), "mdy_peer_buffer_create")
+            ptrs = [None] * self.tp
+            ptrs[self.rank] = self._own.value
+            if self.tp > 1:
+                handles = [None] * self.tp
+                dist.all_gather_object(handles, handle.raw, group=group)
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        continue
+                    p = ctypes.c_void_p()
+                    _C.check(lib.mdy_peer_buffer_open(ctypes.create_string_buffer(h, 64), ctypes.byref(p)),
+                             f"mdy_peer_buffer_open(rank {r})")
+                    self._opened.append(p.value)
+                    ptrs[r] = p.value
+                dist.barrier(group=group)   # nobody launches before every rank has mapped every buffer
+        self.ptrs = (ctypes.c_void_p * self.tp)(*ptrs)
+
+    def next_epoch(self):
+        self.epoch = self.epoch + 1 if self.epoch < 0xFFFFFFFF else 1
+        return self.epoch
+
+    def close(self):
+        """Unmap the peers' buffers and free this rank's.  Call on every rank once no kernel uses them."""
+        lib = _C.lib()
+        with torch.cuda.device(self.device):
+            torch.cuda.synchronize(self.device)
+            for p in self._opened:
+                lib.mdy_peer_buffer_close(p)
+            self._opened = []
+            if self.tp > 1 and dist.is_initialized():
+                dist.barrier(group=self.group)   # a buffer is freed only after every peer has unmapped it
+            if self._own.value:
+                lib.mdy_peer_buffer_destroy(self._own)
+                self._own.value = None
+
+
+def fused_loss_and_grad(lg, lb, dlogits, inv_n, exchange: PeerExchange):
+    """One launch of ``mdy_ce_vp_fused`` for this rank's shard ``lg`` [M, Vs]: writes ``dlogits`` (may be
+    ``lg``) scaled by ``inv_n`` (float32 device scalar) and returns (losses[M], lse[M])."""
+    import ctypes
+    dev = _C.require_cuda(lg, lb, dlogits)
+    m, v = lg.shape
+    if v != exchange.shard_cols or m > exchange.max_rows or lg.dtype != exchange.dtype:
+        raise ValueError("the PeerExchange was created for another shard shape")
+    losses = torch.empty(m, dtype=torch.float32, device=dev)
+    lse = torch.empty(m, dtype=torch.float32, device=dev)
+    one = lambda t: (ctypes.c_void_p * 1)(t.data_ptr())
+    with torch.cuda.device(dev):
+        _C.check(_C.lib().mdy_ce_vp_fused(one(lg), one(dlogits), one(losses), one(lse), exchange.ptrs, _C.ptr(lb),
+                                          _C.ptr(inv_n), 1.0, m, v, lg.stride(0) if m > 1 else v, exchange.tp,
+                                          exchange.rank, 1, exchange.max_rows, exchange.next_epoch(),
+                                          _C.dtype_code(lg), _C.stream_ptr(dev)), "mdy_ce_vp_fused")
+    return losses, lse
+
+
+class _FusedVocabParallelLoss(torch.autograd.Function):
+    """Scalar ``sum(losses) / n_items`` on vocab-sharded logits whose forward already wrote the gradient."""
+
+    @staticmethod
+    def forward(ctx, logits, labels, n_items, exchange, inplace):
+        lg, lb = _ce._flat(logits, labels)
+        dev = lg.device
+        if n_items is None:
+            n = torch.count_nonzero(lb != _ce.IGNORE_INDEX).to(torch.float32)
+        else:
+            n = torch.as_tensor(n_items, device=dev).to(torch.float32)
+        inv = n.reciprocal().reshape(1)
+        dlogits = lg if inplace else torch.empty_like(lg)
+        losses, _ = fused_loss_and_grad(lg, lb, dlogits, inv, exchange)
+        ctx.save_for_backward(dlogits)
+        ctx.input_shape = logits.shape
+        ctx.consumed = False
+        return losses.sum() * inv[0]
+
+    @staticmethod
+    def backward(ctx, dloss):
+        if ctx.consumed:
+            raise RuntimeError("the one-kernel vocab-parallel loss hands its gradient buffer out once")
+        ctx.consumed = True
+        (dlogits,) = ctx.saved_tensors
+        dev = dlogits.device
+        g = dloss.detach().to(device=dev, dtype=torch.float32).reshape(1).contiguous()
+        with torch.cuda.device(dev):
+            _C.check(_C.lib().mdy_scale_inplace(_C.ptr(dlogits), dlogits.numel(), _C.ptr(g),
+                                                _C.dtype_code(dlogits), _C.stream_ptr(dev)), "mdy_scale_inplace")
+        return dlogits.view(ctx.input_shape), None, None, None, None
+
+
 def vocab_parallel_cross_entropy(logits, labels, group=None, inplace=False):
     """Per-row losses for vocab-sharded ``logits`` [..., V/g] and replicated ``labels`` [...]
     (global vocabulary ids, -100 = ignored).  Identical on every rank of ``group``."""
     return _VocabParallelCrossEntropy.apply(logits, labels, group, inplace)
 
 
-def vocab_parallel_entropy_loss(logits, labels, num_items_in_batch=None, group=None, inplace=False):
-    """Scalar ``sum(losses) / num_items_in_batch`` on vocab-sharded logits (same on every rank)."""
+def vocab_parallel_entropy_loss(logits, labels, num_items_in_batch=None, group=None, inplace=False, exchange=None):
+    """Scalar ``sum(losses) / num_items_in_batch`` on vocab-sharded logits (same on every rank).  With a
+    :class:`PeerExchange` (and gradients enabled, logits not float16) the loss and the gradient come from
+    one kernel per GPU that exchanges the row statistics through peer memory; otherwise from the
+    sweep -> all-gather -> sweep path."""
+    if (exchange is not None and torch.is_grad_enabled() and logits.requires_grad
+            and logits.dtype != torch.float16):
+        return _FusedVocabParallelLoss.apply(logits, labels, num_items_in_batch, exchange, bool(inplace))
     losses = vocab_parallel_cross_entropy(logits, labels, group, inplace)
     if num_items_in_batch is None:
         num_items_in_batch = torch.count_nonzero(labels != _ce.IGNORE_INDEX)

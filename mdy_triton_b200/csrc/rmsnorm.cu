@@ -97,6 +97,12 @@ __device__ __forceinline__ void load_w_vec(const void* w, int v, int w_dtype, bo
   }
 }
 
+}  // namespace
+}  // namespace mdy
+#include "rmsnorm_staged.cuh"
+namespace mdy {
+namespace {
+
 template <typename T, int VPT, bool ADD, int MAXT>
 __global__ void __launch_bounds__(MAXT)
 norm_fwd_vec(const T* __restrict__ x, const T* __restrict__ res, const void* __restrict__ w,
@@ -454,24 +460,66 @@ inline int64_t scalar_grid(int64_t M) {
 struct BwdPlan {
   RowPlan p;      // p.vpt == 0: scalar kernel
   int64_t grid;   // CTAs = partial rows written
+  StagedPlan sp;  // sp.ok: the shared-memory-staged kernel runs instead, with `vpl` vectors per lane
+  int vpl;
 };
 
+// Which backward kernel serves a shape: 0 = choose (staged for rows of 6 KB and more with enough of them to
+// fill the GPU), 1 = register-resident kernels always, 2 = staged wherever it has a geometry.
+inline bool want_staged(int64_t M, int64_t row_bytes, int rows_per_block) {
+  const int impl = tunable(MDY_TUNE_NORM_IMPL);
+  if (impl == 1) return false;
+  if (impl == 2) return true;
+  return row_bytes >= 6 * 1024 && M >= (int64_t)rows_per_block * num_sms();
+}
+
+inline int64_t staged_grid(int64_t M, const StagedPlan& sp) {
+  const int64_t blocks = ceil_div(M, (int64_t)(kStagedWarps / sp.team));
+  int per_sm = tunable(MDY_TUNE_NORM_CTAS_PER_SM);
+  if (per_sm <= 0 || per_sm > sp.ctas_per_sm) per_sm = sp.ctas_per_sm;
+  const int64_t cap = (int64_t)num_sms() * per_sm;
+  return blocks < cap ? blocks : (cap > 0 ? cap : 1);
+}
+
 template <typename T>
-inline BwdPlan plan_bwd(int64_t M, int64_t N, bool vec_ok) {
+inline BwdPlan plan_bwd(int64_t M, int64_t N, bool vec_ok, int streams) {
   constexpr int VE = VecInfo<T>::kElems;
-  BwdPlan b{RowPlan{0, 0, 0, 0}, 0};
-  if (vec_ok && N % VE == 0)
+  BwdPlan b{RowPlan{0, 0, 0, 0}, 0, StagedPlan{false, 0, 0, 0, 0, 0}, 0};
+  if (vec_ok && N % VE == 0) {
     b.p = plan_rows(N / VE, bwd_min_threads(), tunable(MDY_TUNE_NORM_BWD_VPT), tunable(MDY_TUNE_NORM_BWD_GROUP));
+    if (M > 0 && sizeof(T) == 2) {   // the staged kernels are built for the 16-bit activation types
+      StagedPlan sp = plan_staged(N * (int64_t)sizeof(T), streams, tunable(MDY_TUNE_NORM_TEAM));
+      const int64_t need = sp.ok ? ceil_div(N / VE, 32 * sp.team) : 99;
+      if (sp.ok && need <= 16 && want_staged(M, N * (int64_t)sizeof(T), kStagedWarps / sp.team)) {
+        b.sp = sp;
+        b.vpl = need <= 2 ? 2 : need <= 4 ? 4 : need <= 8 ? 8 : 16;
+      }
+    }
+  }
   if (M == 0) b.grid = 0;
+  else if (b.sp.ok) b.grid = staged_grid(M, b.sp);
   else b.grid = b.p.vpt ? vec_grid(M, b.p, bwd_per_sm(b.p)) : scalar_grid(M);
   return b;
 }
 
-// Upper bound over both kernels (the caller sizes its scratch before alignment is known).
+// Upper bound over the kernels that may serve the shape (the caller sizes its scratch before alignment
+// and the number of gradient streams are known).
 template <typename T>
 inline int64_t partial_rows(int64_t M, int64_t N) {
-  const int64_t a = plan_bwd<T>(M, N, true).grid, b = plan_bwd<T>(M, N, false).grid;
-  return a > b ? a : b;
+  int64_t rows = plan_bwd<T>(M, N, false, 2).grid;
+  for (int streams = 2; streams <= 3; ++streams) {
+    const int64_t g = plan_bwd<T>(M, N, true, streams).grid;
+    if (g > rows) rows = g;
+  }
+  // the register-resident kernels, should a launch not get the staged one
+  if (N % VecInfo<T>::kElems == 0 && M > 0) {
+    RowPlan p = plan_rows(N / VecInfo<T>::kElems, bwd_min_threads(), tunable(MDY_TUNE_NORM_BWD_VPT), tunable(MDY_TUNE_NORM_BWD_GROUP));
+    if (p.vpt) {
+      const int64_t g = vec_grid(M, p, bwd_per_sm(p));
+      if (g > rows) rows = g;
+    }
+  }
+  return rows;
 }
 
 template <typename T, bool ADD>
@@ -534,6 +582,27 @@ int launch_bwd(const BwdPlan& plan, const void* dy_, const void* x_, const void*
   const bool wvec = aligned16(w);
   if (M == 0) {
     // nothing to sweep: the reduce below writes dw = 0
+  } else if (plan.sp.ok) {
+    if constexpr (sizeof(T) == 2) {
+      StagedBwdArgs a;
+      a.dy = dy; a.x = x; a.dres = ADD ? dres : nullptr; a.w = w; a.w_dtype = w_dtype; a.rstd = rstd; a.dx = dx;
+      a.dw_partial = dw_partial; a.M = M; a.N = (int)N; a.dy_rs = dy_rs; a.x_rs = x_rs; a.dres_rs = dres_rs; a.dx_rs = dx_rs;
+      a.team = plan.sp.team; a.stage_bytes = (int)plan.sp.stage_bytes; a.wait_tries = 1 << 20;
+#define MDY_SBWD(V)                                                                                          \
+  {                                                                                                          \
+    auto kern = norm_bwd_staged<T, V, ADD>;                                                                  \
+    cudaError_t e_ = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)plan.sp.smem); \
+    if (e_ != cudaSuccess) return (int)e_;                                                                   \
+    kern<<<(unsigned)grid, kStagedThreads, plan.sp.smem, st>>>(a);                                           \
+  }
+      switch (plan.vpl) {
+        case 2: MDY_SBWD(2) break;
+        case 4: MDY_SBWD(4) break;
+        case 8: MDY_SBWD(8) break;
+        default: MDY_SBWD(16) break;
+      }
+#undef MDY_SBWD
+    }
   } else if (p.vpt) {
     const size_t sh = (2 * (p.BT / 32) + (p.gpc > 1 ? N : 0)) * sizeof(float);
 #define MDY_BWD(V, MT)                                                                          \
@@ -602,6 +671,10 @@ inline float* noalloc_scratch(cudaError_t* err) {
 }  // namespace
 }  // namespace mdy
 
+namespace mdy {
+int norm_dev_error(bool clear) { return read_dev_error(clear); }
+}  // namespace mdy
+
 using namespace mdy;
 
 extern "C" {
@@ -642,7 +715,7 @@ int mdy_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* r
   if (dy_row_stride < 0 || x_row_stride < N || dx_row_stride < N) return MDY_ERR_SIZE;
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
-    const BwdPlan plan = plan_bwd<T>(M, N, bwd_vec_ok<T>(dy, x, nullptr, dx, N, dy_row_stride, x_row_stride, 0, dx_row_stride));
+    const BwdPlan plan = plan_bwd<T>(M, N, bwd_vec_ok<T>(dy, x, nullptr, dx, N, dy_row_stride, x_row_stride, 0, dx_row_stride), 2);
     return launch_bwd<T, false>(plan, dy, x, w, w_dtype, rstd, nullptr, dx, dw, dw_partial, M, N,
                                 dy_row_stride, x_row_stride, 0, dx_row_stride, (cudaStream_t)stream);
   });
@@ -660,7 +733,7 @@ int mdy_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const 
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
     // the grid is fixed here, once, and the same value is checked against the scratch and launched
-    const BwdPlan plan = plan_bwd<T>(M, N, bwd_vec_ok<T>(dy, x, nullptr, dx, N, dy_row_stride, x_row_stride, 0, dx_row_stride));
+    const BwdPlan plan = plan_bwd<T>(M, N, bwd_vec_ok<T>(dy, x, nullptr, dx, N, dy_row_stride, x_row_stride, 0, dx_row_stride), 2);
     if (plan.grid * N > kNoAllocFloats) return (int)MDY_ERR_UNSUPPORTED;  // would not fit the fixed scratch
     cudaError_t err;
     float* scratch = noalloc_scratch(&err);
@@ -698,7 +771,7 @@ int mdy_add_rmsnorm_bwd(const void* dy, const void* dnew_res, const void* new_re
   if (row_stride < N) return MDY_ERR_SIZE;
   return dispatch_dtype(dtype, [&](auto tag) {
     using T = decltype(tag);
-    const BwdPlan plan = plan_bwd<T>(M, N, bwd_vec_ok<T>(dy, new_res, dnew_res, dx, N, row_stride, row_stride, row_stride, row_stride));
+    const BwdPlan plan = plan_bwd<T>(M, N, bwd_vec_ok<T>(dy, new_res, dnew_res, dx, N, row_stride, row_stride, row_stride, row_stride), dnew_res ? 3 : 2);
     return launch_bwd<T, true>(plan, dy, new_res, w, w_dtype, rstd, dnew_res, dx, dw, dw_partial, M, N,
                                row_stride, row_stride, row_stride, row_stride, (cudaStream_t)stream);
   });

@@ -26,4 +26,9 @@
 #define MDY_TUNE_NORM_FWD_GROUP 17      /* threads per row of the norm forward (rounded up to a warp multiple) */
 #define MDY_TUNE_NORM_BWD_GROUP 18      /* the same for the norm backward */
 #define MDY_TUNE_NORM_FWD_THREADS 19    /* CTA size the norm forward aims for: 128, 256 or 512 */
-#define MDY_TUNE_COUNT 20
+#define MDY_TUNE_NORM_IMPL 20           /* 0 choose, 1 register-resident norm kernels always, 2 shared-memory-staged wherever possible */
+#define MDY_TUNE_CE_VP_CTAS_PER_SM 21   /* CTAs per SM of the one-kernel vocab-parallel cross-entropy */
+#define MDY_TUNE_CE_VP_SLOTS 22         /* its shared-memory slots per CTA (3 or 4) */
+#define MDY_TUNE_RESERVED_23 23         /* unused */
+#define MDY_TUNE_NORM_TEAM 24           /* staged norm kernels: warps per row (1, 2 or 4; 0 = choose) */
+#define MDY_TUNE_COUNT 25

@@ -31,9 +31,12 @@ cfg_cls, model_cls = {{"llama": (transformers.LlamaConfig, transformers.LlamaFor
                       "qwen2": (transformers.Qwen2Config, transformers.Qwen2ForCausalLM),
                       "mistral": (transformers.MistralConfig, transformers.MistralForCausalLM),
                       "phi3": (transformers.Phi3Config, transformers.Phi3ForCausalLM),
+                      "phi3_partial_rotary": (transformers.Phi3Config, transformers.Phi3ForCausalLM),
                       "glm": (transformers.GlmConfig, transformers.GlmForCausalLM),
                       "qwen2_vl": (transformers.Qwen2VLConfig, transformers.Qwen2VLForConditionalGeneration)}}[family]
-extra = {{"pad_token_id": 0}} if family in ("phi3", "glm") else {{}}
+extra = {{"pad_token_id": 0}} if family in ("phi3", "phi3_partial_rotary", "glm") else {{}}
+if family == "phi3_partial_rotary":
+    extra.update(partial_rotary_factor=0.75)   # rotary_dim 48 of head_dim 64, as the Phi-4-mini family configures it
 if family == "glm":
     extra.update(head_dim=64, partial_rotary_factor=0.5)
 text = dict(hidden_size=256, intermediate_size=512, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
@@ -100,7 +103,7 @@ def _run(family, patched, dtype):
     return res
 
 
-@pytest.mark.parametrize("family", ["llama", "qwen2", "mistral", "phi3", "qwen2_vl", "glm"])
+@pytest.mark.parametrize("family", ["llama", "qwen2", "mistral", "phi3", "phi3_partial_rotary", "qwen2_vl", "glm"])
 def test_patched_model_matches_stock_model_fp32(family):
     a = _run(family, False, "float32")
     b = _run(family, True, "float32")

@@ -215,6 +215,29 @@ def test_rope_vs_oracle(b, l, qh, kh, d, theta, dt, batch_cs):
     assert_close(qe, hq, r, "q vs HF eager")
 
 
+@pytest.mark.parametrize("d,rd", [(128, 96), (64, 32), (96, 48), (80, 20)])
+def test_rope_partial_rotary_dim(d, rd):
+    """cos/sin narrower than the head (HuggingFace Phi3 / GLM partial_rotary_factor): the first rotary_dim
+    columns of every head are rotated, the others pass through, forward and backward."""
+    gen = g(d * 7 + rd)
+    b, l, qh, kh = 2, 33, 6, 2
+    q = torch.randn(b, l, qh, d, generator=gen).to(torch.bfloat16); k = torch.randn(b, l, kh, d, generator=gen).to(torch.bfloat16)
+    dq = torch.randn(b, qh, l, d, generator=gen).to(torch.bfloat16); dk = torch.randn(b, kh, l, d, generator=gen).to(torch.bfloat16)
+    cos, sin = E.rope_cos_sin(torch.arange(l)[None], rd, 1e4, torch.bfloat16)
+    qs, ks = leaf(q), leaf(k)
+    qe, ke = core.fused_apply_rope((qs * 1.0).transpose(1, 2), (ks * 1.0).transpose(1, 2), cos.to(DEV), sin.to(DEV))
+    qv, kv = qe.detach().clone(), ke.detach().clone()
+    torch.autograd.backward([qe, ke], [dq.to(DEV), dk.to(DEV)])
+    qt, kt = q.transpose(1, 2), k.transpose(1, 2)
+    qo, ko = E.rope_fwd(qt[..., :rd], kt[..., :rd], cos, sin)
+    gq, gk = E.rope_bwd(dq[..., :rd], dk[..., :rd], cos, sin)
+    assert_close(qv[..., :rd], qo, 1e-2, "q rotated part"); assert_close(kv[..., :rd], ko, 1e-2, "k rotated part")
+    assert torch.equal(qv[..., rd:].cpu(), qt[..., rd:]) and torch.equal(kv[..., rd:].cpu(), kt[..., rd:])
+    assert_close(qs.grad.transpose(1, 2)[..., :rd], gq, 1e-2, "dq rotated part")
+    assert_close(ks.grad.transpose(1, 2)[..., :rd], gk, 1e-2, "dk rotated part")
+    assert torch.equal(qs.grad.transpose(1, 2)[..., rd:].cpu(), dq[..., rd:]) and torch.equal(ks.grad.transpose(1, 2)[..., rd:].cpu(), dk[..., rd:])
+
+
 def test_rope_head_major_storage_and_unsqueeze_dim_2():
     """q/k stored [B, H, L, D] (head-major) go through the strided path; unsqueeze_dim=2 means the caller's
     tensors are [B, L, H, D]."""
@@ -621,8 +644,10 @@ def test_ce_cluster_launch_geometry():
     assert (c, nt) == (1, 256) and ncl == 3 * sms and smem < 66 * 1024
     c, ncl, nt, smem = geometry(3, 128256)             # fewer rows than co-resident clusters
     assert (c, ncl) == (2, 3)
-    c, ncl, nt, smem = geometry(64, 128256, torch.float32)   # 501 KB rows: three CTAs per row
-    assert c == 3 and ncl <= sms // 3
+    c, ncl, nt, smem = geometry(64, 128256, torch.float32)   # 501 KB rows: clusters of eight small CTAs, three per SM
+    assert (c, nt) == (8, 256) and ncl <= 3 * sms // 8 and smem < 70 * 1024
+    c, ncl, nt, smem = geometry(64, 98304, torch.float32)    # 384 KB rows: still two 192 KB slices, one CTA per SM
+    assert (c, nt) == (2, 512)
     assert lib.mdy_last_device_error(1) == 0
 
 

@@ -54,7 +54,10 @@ def _install_oracle_hooks():
 def _gloo_worker(rank, world, port, fail_rank, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     import datetime
-    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=8))
+    # a short limit only where a rank is going to fail on purpose (its peers must notice quickly); otherwise a
+    # generous one, so that slow process start-up on a loaded machine is not mistaken for a failure
+    limit = 8 if fail_rank >= 0 else 120
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=limit))
     try:
         _install_oracle_hooks()
         from mdy_triton_b200.core.vocab_parallel import vocab_parallel_cross_entropy, vocab_parallel_entropy_loss
@@ -101,7 +104,7 @@ def _run_gloo(world, fail_rank=-1):
     for p in procs:
         p.start()
     for p in procs:
-        p.join(60)
+        p.join(240)
         if p.is_alive():
             p.kill()
     return dict(out)
@@ -171,6 +174,25 @@ def _nccl_worker(rank, world, port, out):
         full = E.ce_grad(lg, lb, fs, dl)[:, rank * v:(rank + 1) * v]
         g = shard.grad.float().cpu()
         ok = torch.allclose(losses.cpu(), fl, rtol=1e-4, atol=1e-4) and bool(((g - full).abs() <= 1e-2 * (full.abs() + full.abs().mean())).all())
+        # the one-kernel path: records stored straight into the peer's exchange buffer (mapped through CUDA IPC),
+        # two calls in a row on the same buffers
+        from mdy_triton_b200.core.vocab_parallel import PeerExchange, vocab_parallel_entropy_loss
+        from mdy_triton_b200 import _C
+        ex = PeerExchange(lg.shape[0], v, torch.bfloat16, dev)
+        try:
+            n = int((lb != -100).sum())
+            want = E.ce_grad(lg, lb, fs, torch.tensor(1.0 / n))[:, rank * v:(rank + 1) * v]
+            for _ in range(2):
+                leaf = lg[:, rank * v:(rank + 1) * v].contiguous().to(dev).requires_grad_(True)
+                loss = vocab_parallel_entropy_loss(leaf, lb.to(dev), exchange=ex)
+                loss.backward()
+                torch.cuda.synchronize()
+                g2 = leaf.grad.float().cpu()
+                ok = (ok and abs(float(loss) - float(fl.sum() / n)) <= 1e-4 * max(1.0, float(fl.sum() / n))
+                      and bool(((g2 - want).abs() <= 1e-2 * (want.abs() + want.abs().mean())).all())
+                      and _C.lib().mdy_last_device_error(1) == 0)
+        finally:
+            ex.close()
         out[rank] = "ok" if ok else "mismatch"
     except Exception as e:  # noqa: BLE001
         out[rank] = f"error: {type(e).__name__}: {e}"
@@ -193,3 +215,134 @@ def test_two_nccl_ranks_when_two_gpus_are_present():
         if p.is_alive():
             p.kill()
     assert dict(out) == {0: "ok", 1: "ok"}
+
+
+# ------------------------------------------------------------------ the one-kernel path (mdy_ce_vp_fused)
+def _fused_all_ranks_one_gpu(lib, shards, outs, labels, inv_n, xbufs, xrows, epoch):
+    """All ranks' shards as virtual ranks of ONE launch on one GPU (the form the exchange takes where there
+    are fewer GPUs than ranks).  Returns per-rank (losses, lse)."""
+    import ctypes
+    from mdy_triton_b200 import _C
+    tp = len(shards)
+    m, vs = shards[0].shape
+    dev = shards[0].device
+    losses = [torch.full((m,), float("nan"), device=dev) for _ in range(tp)]
+    lse = [torch.full((m,), float("nan"), device=dev) for _ in range(tp)]
+    arr = lambda ts: (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])
+    rc = lib.mdy_ce_vp_fused(arr(shards), arr(outs), arr(losses), arr(lse), arr(xbufs), labels.data_ptr(), inv_n.data_ptr(),
+                             1.0, m, vs, vs, tp, 0, tp, xrows, epoch, _C.dtype_code(shards[0]),
+                             torch.cuda.current_stream().cuda_stream)
+    return rc, losses, lse
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("v,tp,sigma,dt,m", [
+    (32000, 8, 1.0, torch.bfloat16, 300),     # 8 KB slices: four small CTAs per SM
+    (128256, 8, 4.0, torch.bfloat16, 200),    # 32 KB slices
+    (128256, 2, 4.0, torch.bfloat16, 120),    # 128 KB shard rows: four column slices per rank
+    (151936, 4, 1.0, torch.bfloat16, 150),
+    (256000, 8, 4.0, torch.bfloat16, 100),    # 64 KB shard rows: two slices per rank, 16 participants
+    (128256, 1, 3.0, torch.bfloat16, 160),    # one rank: the exchange is between column slices only
+    (8192, 4, 1.0, torch.float32, 64),
+    (32000, 4, 2.0, torch.float16, 64),
+])
+def test_one_kernel_exchange_all_ranks_on_one_gpu(v, tp, sigma, dt, m):
+    """mdy_ce_vp_fused against the full-vocabulary oracle: losses, lse and every rank's gradient columns, on two
+    calls in a row with different logits (the exchange buffers keep the previous call's records, told apart by
+    the epoch), the second one in place."""
+    from mdy_triton_b200 import _C
+    lib = _C.lib()
+    dev = torch.device("cuda", 0)
+    vs = v // tp
+    xrows = 512
+    nbytes = lib.mdy_ce_vp_exchange_bytes(xrows, vs, tp, _C.DTYPE_CODE[dt])
+    assert nbytes > 0
+    xbufs = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(tp)]
+    rel = 1e-2 if dt != torch.float32 else 1e-4
+    atol = 2.0 ** -24 if dt == torch.float16 else 0.0
+    for call, inplace in ((1, False), (2, True)):
+        g = torch.Generator().manual_seed(100 * call + tp)
+        lg = (torch.randn(m, v, generator=g) * sigma).to(dt)
+        lb = torch.randint(0, v, (m,), generator=g); lb[torch.rand(m, generator=g) < 0.05] = -100
+        n = int((lb != -100).sum())
+        inv_n = torch.full((1,), 1.0 / n, device=dev)
+        shards = [lg[:, r * vs:(r + 1) * vs].contiguous().to(dev) for r in range(tp)]
+        outs = shards if inplace else [torch.full_like(s, float("nan")) for s in shards]
+        rc, losses, lse = _fused_all_ranks_one_gpu(lib, shards, outs, lb.to(dev), inv_n, xbufs, xrows, call)
+        assert rc == 0, _C.status_string(rc)
+        torch.cuda.synchronize()
+        assert lib.mdy_last_device_error(1) == 0
+        fl, fs = E.ce_rows(lg, lb)
+        full = E.ce_grad(lg, lb, fs, torch.tensor(1.0 / n))
+        for r in range(tp):
+            assert torch.allclose(losses[r].cpu(), fl, rtol=LOSS_TOL, atol=LOSS_TOL), f"losses of rank {r}, call {call}"
+            assert torch.allclose(lse[r].cpu(), fs, rtol=LOSS_TOL, atol=LOSS_TOL), f"lse of rank {r}, call {call}"
+            assert_close(outs[r], full[:, r * vs:(r + 1) * vs], rel, f"gradient of rank {r}, call {call}", atol)
+
+
+@pytest.mark.gpu
+def test_one_kernel_exchange_gives_up_on_a_missing_record_and_poisons_the_loss():
+    """Failure detection without a fault: a test hook keeps one participant from publishing row 0 and shortens
+    the bound of the poll, so every rank's wait for that record runs out.  The launch returns, the flag reads 2,
+    row 0 has NaN loss on every rank while the other rows are right, and the next call is clean."""
+    import time
+    from mdy_triton_b200 import _C
+    lib = _C.lib()
+    dev = torch.device("cuda", 0)
+    m, v, tp, dt = 64, 32000, 4, torch.bfloat16
+    vs = v // tp
+    nbytes = lib.mdy_ce_vp_exchange_bytes(m, vs, tp, _C.DTYPE_CODE[dt])
+    xbufs = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(tp)]
+    g = torch.Generator().manual_seed(5)
+    lg = (torch.randn(m, v, generator=g) * 2).to(dt); lb = torch.randint(0, v, (m,), generator=g)
+    inv_n = torch.full((1,), 1.0 / m, device=dev)
+    shards = [lg[:, r * vs:(r + 1) * vs].contiguous().to(dev) for r in range(tp)]
+    fl, fs = E.ce_rows(lg, lb)
+    torch.cuda.synchronize()
+    assert lib.mdy_last_device_error(1) == 0
+    _C.set_tunable(_C.TUNE_CE_WAIT_TEST, 2)      # participant 1 (rank 1, slice 0) stays silent on row 0
+    try:
+        t0 = time.perf_counter()
+        rc, losses, _ = _fused_all_ranks_one_gpu(lib, shards, [torch.empty_like(s) for s in shards], lb.to(dev), inv_n, xbufs, m, 1)
+        torch.cuda.synchronize()
+        elapsed = time.perf_counter() - t0
+    finally:
+        _C.set_tunable(_C.TUNE_CE_WAIT_TEST, 0)
+    assert rc == 0 and elapsed < 2.0
+    assert lib.mdy_last_device_error(1) == 2
+    for r in range(tp):
+        got = losses[r].cpu()
+        assert torch.isnan(got[0])
+        healthy = ~torch.isnan(got)
+        assert healthy.sum() >= m // 2 and torch.allclose(got[healthy], fl[healthy], rtol=LOSS_TOL, atol=LOSS_TOL)
+    outs = [torch.empty_like(s) for s in shards]
+    rc, losses, lse = _fused_all_ranks_one_gpu(lib, shards, outs, lb.to(dev), inv_n, xbufs, m, 2)
+    torch.cuda.synchronize()
+    assert rc == 0 and lib.mdy_last_device_error(1) == 0
+    full = E.ce_grad(lg, lb, fs, torch.tensor(1.0 / m))
+    for r in range(tp):
+        assert torch.allclose(losses[r].cpu(), fl, rtol=LOSS_TOL, atol=LOSS_TOL)
+        assert_close(outs[r], full[:, r * vs:(r + 1) * vs], 1e-2, f"rank {r} after the expired wait")
+
+
+@pytest.mark.gpu
+def test_peer_exchange_object_and_fused_loss_single_rank():
+    """The public path with one rank: PeerExchange set-up (library-allocated buffer, IPC handle) and
+    vocab_parallel_entropy_loss(exchange=...) against the one-pass single-GPU loss."""
+    from mdy_triton_b200.core import vocab_parallel as vp
+    import mdy_triton.core as core
+    dev = torch.device("cuda", 0)
+    g = torch.Generator().manual_seed(8)
+    m, v = 256, 128256
+    lg = (torch.randn(m, v, generator=g) * 3).to(torch.bfloat16).to(dev); lb = torch.randint(0, v, (m,), generator=g).to(dev)
+    lb[::11] = -100
+    ex = vp.PeerExchange(m, v, torch.bfloat16, dev)
+    try:
+        for _ in range(2):
+            a = lg.clone().requires_grad_(True); b = lg.clone().requires_grad_(True)
+            la = vp.vocab_parallel_entropy_loss(a, lb, exchange=ex); la.backward()
+            lb_ = core.triton_entropy_loss(b, lb); lb_.backward()
+            assert abs(float(la) - float(lb_)) <= LOSS_TOL * max(1.0, abs(float(lb_)))
+            assert_close(a.grad, b.grad, 1e-2, "gradient")
+    finally:
+        ex.close()
