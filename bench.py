@@ -764,6 +764,17 @@ def run_single_op(args):
         phases = [lambda: _C.check(lib.mdy_ce_fused(lg.data_ptr(), out.data_ptr(), lb.data_ptr(), losses.data_ptr(), lse.data_ptr(),
                                                     inv.data_ptr(), 1.0, M, V, V, bf, st), "ce")]
         nbytes = [2 * M * V * 2]
+    elif op == "vp":
+        # the one-kernel vocab-parallel cross-entropy on ONE rank: `--vocab` is the shard width, so this is the
+        # per-GPU work of a sharded vocabulary without the peers (the exchange runs through this GPU's own buffer)
+        from mdy_triton_b200.core import vocab_parallel as vp
+        V = args.vocab or cfg["vocab"] // 8
+        lg = rn(M, V).mul_(3)
+        lb = torch.randint(0, V, (M,), device=dev, generator=g)
+        inv = torch.tensor([1.0 / M], device=dev)
+        exchange = vp.PeerExchange(M, V, torch.bfloat16, dev)
+        phases = [lambda: vp.fused_loss_and_grad(lg, lb, lg, inv, exchange)]
+        nbytes = [2 * M * V * 2]
     else:
         raise SystemExit(f"unknown operator {op!r}")
 
@@ -861,7 +872,7 @@ def main():
                     help="opset (default): the fused operator set; llama1b: only the Llama-1B training step with the patch; "
                          "llama1b-fused-residual: the same with each layer's closing residual add fused into the next RMSNorm; "
                          "llama1b-unpatched: the same with stock HuggingFace modules; vpce: only the vocab-parallel sweep; "
-                         "op:NAME: one operator (norm, rmsnorm, rope, swiglu, ce, ce2)")
+                         "op:NAME: one operator (norm, rmsnorm, rope, swiglu, ce, ce2, vp)")
     ap.add_argument("--profile-share", action="store_true",
                     help="llama1b workloads: after timing, profile two more steps and report the share of GPU kernel time spent in the fused kernels")
     ap.add_argument("--ddp-bucket-mb", type=int, default=200, help="DDP gradient bucket size for the llama1b workloads")

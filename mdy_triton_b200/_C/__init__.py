@@ -41,6 +41,7 @@ TUNE_NORM_FWD_THREADS = 19
 TUNE_NORM_IMPL = 20
 TUNE_CE_VP_CTAS_PER_SM = 21
 TUNE_CE_VP_SLOTS = 22
+TUNE_CE_VP_SLICE_KB = 23
 TUNE_NORM_TEAM = 24
 
 _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float

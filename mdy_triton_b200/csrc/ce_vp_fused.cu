@@ -362,15 +362,17 @@ inline bool vp_geometry(int64_t vs, int esize, int tp, VpGeometry* out) {
   const int64_t nvec = vs / ve;
   const int64_t row_bytes = nvec * 16;
   VpGeometry g;
-  g.nsub = (int)ceil_div(row_bytes, 32 * 1024);
+  int slice_kb = tunable(MDY_TUNE_CE_VP_SLICE_KB);
+  if (slice_kb < 4 || slice_kb > 96) slice_kb = 32;
+  g.nsub = (int)ceil_div(row_bytes, (int64_t)slice_kb * 1024);
   if (g.nsub * tp > kVpMaxParts) return false;
   g.vps = (int)ceil_div(nvec, g.nsub);
   if ((int64_t)(g.nsub - 1) * g.vps >= nvec) return false;  // a slice would be empty
   const int64_t slice_bytes = (int64_t)g.vps * 16;
-  g.nt = slice_bytes <= 10 * 1024 ? 128 : 256;            // compute threads per CTA (plus one exchange warp)
+  g.nt = slice_bytes <= 10 * 1024 ? 128 : slice_bytes <= 40 * 1024 ? 256 : 512;   // compute threads per CTA (plus one exchange warp)
   if (ceil_div(g.vps, g.nt * 4) > kVpMaxChunks) return false;
   // Several CTAs per SM where the slices are small, so that one CTA's barriers are covered by another's sweeps.
-  g.per_sm = g.nt == 128 ? 4 : 2;
+  g.per_sm = g.nt == 128 ? 4 : g.nt == 256 ? 2 : 1;
   if (tunable(MDY_TUNE_CE_VP_CTAS_PER_SM) > 0) g.per_sm = tunable(MDY_TUNE_CE_VP_CTAS_PER_SM);
   g.slot_bytes = (int)((slice_bytes + 127) / 128 * 128);
   const int fixed = kVpBarriers * 8 + (256 + 8) * 4 + kLabRing * 8;
@@ -467,7 +469,8 @@ int mdy_ce_vp_fused(const void* const* logits, void* const* dlogits, float* cons
     if (!vp_geometry(shard_cols, (int)sizeof(T), tp, &g)) return (int)MDY_ERR_UNSUPPORTED;
     a.nsub = g.nsub; a.vps = g.vps; a.slot_bytes = g.slot_bytes; a.nslots = g.nslots; a.lag = g.lag;
     if (g.nt == 128) return launch_vp<T, 128>(a, g, (cudaStream_t)stream);
-    return launch_vp<T, 256>(a, g, (cudaStream_t)stream);
+    if (g.nt == 256) return launch_vp<T, 256>(a, g, (cudaStream_t)stream);
+    return launch_vp<T, 512>(a, g, (cudaStream_t)stream);
   });
 }
 

@@ -29,6 +29,6 @@
 #define MDY_TUNE_NORM_IMPL 20           /* 0 choose, 1 register-resident norm kernels always, 2 shared-memory-staged wherever possible */
 #define MDY_TUNE_CE_VP_CTAS_PER_SM 21   /* CTAs per SM of the one-kernel vocab-parallel cross-entropy */
 #define MDY_TUNE_CE_VP_SLOTS 22         /* its shared-memory slots per CTA (3 or 4) */
-#define MDY_TUNE_RESERVED_23 23         /* unused */
+#define MDY_TUNE_CE_VP_SLICE_KB 23       /* largest column slice of the one-kernel vocab-parallel cross-entropy (KiB, default 32) */
 #define MDY_TUNE_NORM_TEAM 24           /* staged norm kernels: warps per row (1, 2 or 4; 0 = choose) */
 #define MDY_TUNE_COUNT 25

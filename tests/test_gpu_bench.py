@@ -34,7 +34,7 @@ def test_default_workload_line_on_a_small_shard():
 
 
 def test_small_config_is_flushed_and_replayed_from_a_graph():
-    d = _bench("--config", "c1", "--steps", "3", "--no-e2e", "--no-cpu-baseline")
+    d = _bench("--config", "c1", "--steps", "3", "--no-e2e", "--no-cpu-baseline", "--no-extras")
     assert "flush" in json.dumps(d["config"]).lower()
     for op, v in d["per_op"].items():
         assert all(us > 0 for us in v["graph_replay_us"].values()), op
