@@ -64,6 +64,11 @@ int mdy_set_tunable(int id, int value);
  * synchronises with the device, returns the flag (0 = no such event, -1 = the flag could not be
  * read) and resets it when clear != 0.  For tests and diagnostics; not needed on the hot path. */
 int mdy_last_device_error(int clear);
+/* The same flag per kernel family, for diagnosis: source 0 = one-pass cross-entropy (cluster kernel), 1 =
+ * one-kernel vocab-parallel cross-entropy, 2 = staged RMSNorm backward; 16-19 = where the first wait of the
+ * vocab-parallel kernel expired: kind (1 a row slice never arrived, 2 a peer's record, 3 / 4 a hand-off inside
+ * the CTA), CTA, row index within the CTA, thread.  MDY_ERR_ARG for another source. */
+int mdy_device_error_of(int source, int clear);
 /* Launch geometry of the calling thread's most recent cluster-kernel cross-entropy launch: CTAs per
  * cluster, clusters launched (= co-resident clusters, or M if smaller), threads per CTA, dynamic shared
  * memory per CTA.  Any pointer may be NULL.  Returns MDY_ERR_ARG if this thread has not launched one.

@@ -55,6 +55,7 @@ SIGNATURES = {
     "mdy_set_tunable": (_I, [_I, _I]),
     "mdy_get_tunable": (_I, [_I]),
     "mdy_last_device_error": (_I, [_I]),
+    "mdy_device_error_of": (_I, [_I, _I]),
     "mdy_ce_last_geometry": (_I, [_P, _P, _P, _P]),
     "mdy_rowwise_extreme": (_I, [_P, _P, _P, _L, _L, _L, _I, _I, _P]),
     "mdy_rmsnorm_bwd_partial_rows": (_L, [_L, _L, _I]),

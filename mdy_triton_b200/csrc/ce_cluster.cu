@@ -401,8 +401,19 @@ extern "C" int mdy_ce_last_geometry(int* cluster_ctas, int* clusters, int* threa
 namespace mdy {
 int ce_cluster_dev_error(bool clear) { return read_dev_error(clear); }
 int ce_vp_dev_error(bool clear);  // ce_vp_fused.cu
+int ce_vp_dev_detail(int k, bool clear);
 int norm_dev_error(bool clear);   // rmsnorm.cu
 }  // namespace mdy
+
+extern "C" int mdy_device_error_of(int source, int clear) {
+  switch (source) {
+    case 0: return mdy::ce_cluster_dev_error(clear != 0);
+    case 1: return mdy::ce_vp_dev_error(clear != 0);
+    case 2: return mdy::norm_dev_error(clear != 0);
+    case 16: case 17: case 18: case 19: return mdy::ce_vp_dev_detail(source - 16, clear != 0);
+    default: return MDY_ERR_ARG;
+  }
+}
 
 extern "C" int mdy_last_device_error(int clear) {
   const int a = mdy::ce_cluster_dev_error(clear != 0);

@@ -64,6 +64,21 @@ struct VpArgs {
   int mute_part;                    // test hook: participant `mute_part - 1` never publishes row 0 (0 = off)
 };
 
+// Where the first bounded wait of a launch expired: {kind (1 slot data, 3 lse hand-off, 4 statistics hand-off, 2 a
+// peer's record), CTA, row index of the CTA, thread}.  Diagnosis only (mdy_device_error_of, sources 16-19).
+__device__ int g_vp_detail[4] = {0, 0, 0, 0};
+
+__device__ __forceinline__ void note_expiry(int kind, int i) {
+  if (atomicCAS(&g_vp_detail[0], 0, kind) == 0) {
+    g_vp_detail[1] = (int)blockIdx.x; g_vp_detail[2] = i; g_vp_detail[3] = (int)threadIdx.x;
+  }
+}
+__device__ __forceinline__ void vp_wait(int kind, int i, uint32_t bar, uint32_t parity, bool& dead, int tries) {
+  const bool was = dead;
+  mbar_wait(bar, parity, dead, tries);
+  if (!was && dead) note_expiry(kind, i);
+}
+
 __device__ __forceinline__ void st_volatile_v4(uint4* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -83,11 +98,15 @@ __device__ __forceinline__ void bar_arrive_id(int id, int count) {
 // Hand-offs inside a CTA.  Between the compute warps and the exchange warp they are mbarriers, waited for
 // with the same bounded try_wait as the bulk copies, so that a slip in the protocol would show up as an
 // expired wait (flag, NaN loss), never as a hang:
-//   stats[i & 3]  one arrival per compute warp: row i's per-warp statistics are in shared memory
-//   lse[jb & 1]   one arrival by the exchange warp: the global lse of gradient row jb is in shared memory
+//   stats[i & 7]  one arrival per compute warp: row i's per-warp statistics are in shared memory
+//   lse[jb & 3]   one arrival by the exchange warp: the global lse of gradient row jb is in shared memory
+// The compute warps can be at most lag + 1 <= 4 rows ahead of the exchange warp's statistics waits and the
+// exchange warp at most two rows ahead of their lse waits, so rings of 4 and 2 barriers would do; they are
+// twice that, so that a barrier is never re-armed while anyone could still be waiting for its previous phase.
 // Among the compute warps only, hardware barrier kBarSlot: the slice has left shared memory, refill its slot.
 constexpr int kBarSlot = 1;
-constexpr int kVpBarriers = 16;   // 8-byte mbarrier slots reserved: kVpMaxSlots for the ring, 4 stats, 2 lse
+constexpr int kStatsRing = 8, kLseRing = 4;
+constexpr int kVpBarriers = 24;   // 8-byte mbarrier slots reserved: kVpMaxSlots for the ring, the two rings above
 
 // A CTA is NTC compute threads plus ONE exchange warp (warp 0).  The compute warps stream: statistics
 // sweep of row i, gradient sweep of row i - lag, both from shared memory, never waiting for the exchange
@@ -103,11 +122,11 @@ __global__ void __launch_bounds__(NTC + 32) ce_vp_fused_kernel(VpArgs a) {
   constexpr int NTA = NTC + 32;
   extern __shared__ __align__(128) unsigned char smem_raw[];
   uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + (size_t)a.nslots * a.slot_bytes);
-  float* red = reinterpret_cast<float*>(full + kVpBarriers);  // [4][64]: per-warp (max, sum) of a row
-  float* bcast = red + 256;                                    // [2][4]: global lse of a gradient row
+  float* red = reinterpret_cast<float*>(full + kVpBarriers);  // [kStatsRing][64]: per-warp (max, sum) of a row
+  float* bcast = red + kStatsRing * 64;                        // [kLseRing][4]: global lse of a gradient row
   // labels of this CTA's rows, fetched kLabAhead rows ahead by the exchange warp into a ring: a label is
   // never waited for by a compute warp
-  long long* lab_s = reinterpret_cast<long long*>(bcast + 8);  // [kLabRing]
+  long long* lab_s = reinterpret_cast<long long*>(bcast + kLseRing * 4);  // [kLabRing]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int vr = blockIdx.x / a.G, c = blockIdx.x % a.G;
@@ -124,15 +143,15 @@ __global__ void __launch_bounds__(NTC + 32) ce_vp_fused_kernel(VpArgs a) {
   const T* logits = reinterpret_cast<const T*>(a.logits[vr]);
   T* dlogits = reinterpret_cast<T*>(a.dlogits[vr]);
   const uint32_t slots_s = smem_u32(smem_raw), full_s = smem_u32(full);
-  const uint32_t stats_s = full_s + 8 * kVpMaxSlots, lse_s = stats_s + 8 * 4;
+  const uint32_t stats_s = full_s + 8 * kVpMaxSlots, lse_s = stats_s + 8 * kStatsRing;
   const uint32_t parity_x = a.epoch & 1u;
   const int R = rl < a.M ? (a.M - rl + lanes - 1) / lanes : 0;  // rows of this CTA: rl, rl + lanes, ...
   const int nslots = a.nslots, lag = a.lag;
 
   if (tid == 32) {
     for (int k = 0; k < nslots; ++k) mbar_init(full_s + 8 * k, 1);
-    for (int k = 0; k < 4; ++k) mbar_init(stats_s + 8 * k, NWC);
-    for (int k = 0; k < 2; ++k) mbar_init(lse_s + 8 * k, 1);
+    for (int k = 0; k < kStatsRing; ++k) mbar_init(stats_s + 8 * k, NWC);
+    for (int k = 0; k < kLseRing; ++k) mbar_init(lse_s + 8 * k, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (tid < kLabAhead && tid < R) lab_s[tid] = a.labels[(int64_t)rl + (int64_t)tid * lanes];
@@ -183,6 +202,7 @@ __global__ void __launch_bounds__(NTC + 32) ce_vp_fused_kernel(VpArgs a) {
               if (++tries >= a.wait_tries) {
                 dead = true;
                 atomicExch(&g_dev_error, 2);
+                note_expiry(2, jb);
                 break;
               }
               if (tries > 64) __nanosleep(200);
@@ -197,22 +217,22 @@ __global__ void __launch_bounds__(NTC + 32) ce_vp_fused_kernel(VpArgs a) {
           const float xs = warp_sum(nx);
           if (dead) lse_g = NAN;
           if (lane == 0) {
-            bcast[(jb & 1) * 4] = lse_g;
+            bcast[(jb & (kLseRing - 1)) * 4] = lse_g;
             if (sl == 0) { a.losses[vr][row_b] = lse_g + xs; a.lse[vr][row_b] = lse_g; }
           }
         } else if (lane == 0 && sl == 0) {
           a.losses[vr][row_b] = 0.f; a.lse[vr][row_b] = 0.f;
         }
         __syncwarp();
-        if (lane == 0) mbar_arrive(lse_s + 8 * (jb & 1));
+        if (lane == 0) mbar_arrive(lse_s + 8 * (jb & (kLseRing - 1)));
         row_b += lanes;
       }
       // ---- statistics row i: finish the CTA's reduction and publish the record to every rank
       if (i < R) {
         const int64_t label = lab_s[i & (kLabRing - 1)];
-        mbar_wait(stats_s + 8 * (i & 3), (uint32_t)(i >> 2) & 1u, dead, a.wait_tries);
+        vp_wait(4, i, stats_s + 8 * (i & (kStatsRing - 1)), (uint32_t)(i >> 3) & 1u, dead, a.wait_tries);
         if (label != MDY_IGNORE_INDEX) {
-          const float* rd = red + (i & 3) * 64;
+          const float* rd = red + (i & (kStatsRing - 1)) * 64;
           float m = lane < NWC ? rd[lane] : -INFINITY;
           float s = lane < NWC ? rd[32 + lane] : 0.f;
           group_merge<32>(m, s);   // every lane ends up with the slice's (max, sum): lane r publishes to rank r
@@ -256,7 +276,7 @@ __global__ void __launch_bounds__(NTC + 32) ce_vp_fused_kernel(VpArgs a) {
         const uint32_t base = slots_s + (uint32_t)slot_a * a.slot_bytes + my_off;
         float m = -INFINITY, s0 = 0.f, s1 = 0.f;
         if (my_nvec > 0) {
-          mbar_wait(full_s + 8 * slot_a, (phase_bits >> slot_a) & 1u, dead, a.wait_tries);
+          vp_wait(1, i, full_s + 8 * slot_a, (phase_bits >> slot_a) & 1u, dead, a.wait_tries);
           phase_bits ^= 1u << slot_a;
           for (int k = 0; k < nfull; ++k) {
             uint4 q[VPC];
@@ -277,11 +297,11 @@ __global__ void __launch_bounds__(NTC + 32) ce_vp_fused_kernel(VpArgs a) {
         float s = s0 + s1;
         group_merge<32>(m, s);
         if (dead) m = NAN;  // the slice never arrived: the row's record and loss become NaN
-        float* rd = red + (i & 3) * 64;
+        float* rd = red + (i & (kStatsRing - 1)) * 64;
         if (lane == 0) { rd[cw] = m; rd[32 + cw] = s; }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(stats_s + 8 * (i & 3));
+      if (lane == 0) mbar_arrive(stats_s + 8 * (i & (kStatsRing - 1)));
       slot_a = slot_a + 1 == nslots ? 0 : slot_a + 1;
     }
     // ------------------------------------------------- B(i - lag): gradient of row i - lag, refill
@@ -294,13 +314,13 @@ __global__ void __launch_bounds__(NTC + 32) ce_vp_fused_kernel(VpArgs a) {
       const int64_t label_n = jn < R ? lab_s[jn & (kLabRing - 1)] : MDY_IGNORE_INDEX;
       const int64_t row_n = row + (int64_t)nslots * lanes;
       // the exchange warp is done with row jb (usually long since): its lse is in shared memory
-      mbar_wait(lse_s + 8 * (jb & 1), (uint32_t)(jb >> 1) & 1u, dead, a.wait_tries);
+      vp_wait(3, jb, lse_s + 8 * (jb & (kLseRing - 1)), (uint32_t)(jb >> 2) & 1u, dead, a.wait_tries);
       if (label == MDY_IGNORE_INDEX) {
         if (ct == 0) issue_load(slot_b, row_n, label_n);  // the slot was never used by this row
         const uint4 z = make_uint4(0, 0, 0, 0);
         for (int v = ct; v < my_nvec; v += NTC) st_stream(dst + (int64_t)(v - ct) * VE, z);
       } else {
-        const float lse_g = bcast[(jb & 1) * 4];
+        const float lse_g = bcast[(jb & (kLseRing - 1)) * 4];
         const float c2 = -lse_g * kLog2e + log2g;
         const uint32_t base = slots_s + (uint32_t)slot_b * a.slot_bytes + my_off;
         // the label's own element, if it lies in this slice: (p - 1) * g, written after the vector store
@@ -362,8 +382,11 @@ inline bool vp_geometry(int64_t vs, int esize, int tp, VpGeometry* out) {
   const int64_t nvec = vs / ve;
   const int64_t row_bytes = nvec * 16;
   VpGeometry g;
+  // Column slices of at most 32 KB (256 compute threads, two CTAs per SM), or 64 KB for shard rows above 96 KB
+  // (512 compute threads, one CTA per SM: the per-row work that does not scale with the slice is amortised
+  // over twice the logits; measured 0.81 against 0.77 of the copy bandwidth at 250 KB rows).
   int slice_kb = tunable(MDY_TUNE_CE_VP_SLICE_KB);
-  if (slice_kb < 4 || slice_kb > 96) slice_kb = 32;
+  if (slice_kb < 4 || slice_kb > 96) slice_kb = row_bytes > 96 * 1024 ? 64 : 32;
   g.nsub = (int)ceil_div(row_bytes, (int64_t)slice_kb * 1024);
   if (g.nsub * tp > kVpMaxParts) return false;
   g.vps = (int)ceil_div(nvec, g.nsub);
@@ -375,7 +398,7 @@ inline bool vp_geometry(int64_t vs, int esize, int tp, VpGeometry* out) {
   g.per_sm = g.nt == 128 ? 4 : g.nt == 256 ? 2 : 1;
   if (tunable(MDY_TUNE_CE_VP_CTAS_PER_SM) > 0) g.per_sm = tunable(MDY_TUNE_CE_VP_CTAS_PER_SM);
   g.slot_bytes = (int)((slice_bytes + 127) / 128 * 128);
-  const int fixed = kVpBarriers * 8 + (256 + 8) * 4 + kLabRing * 8;
+  const int fixed = kVpBarriers * 8 + (kStatsRing * 64 + kLseRing * 4) * 4 + kLabRing * 8;
   const int budget = (227 * 1024) / g.per_sm - 1024 - fixed;
   g.nslots = budget / g.slot_bytes;
   if (g.nslots > 5) g.nslots = 5;
@@ -395,6 +418,10 @@ int launch_vp(VpArgs a, const VpGeometry& g, cudaStream_t st) {
   auto kern = ce_vp_fused_kernel<T, NTC, 4>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
+  // The occupancy figure below assumes the largest shared-memory carve-out; ask for it, so that the SMs are
+  // not left configured with a smaller one in which fewer CTAs fit than the grid counts on.
+  (void)cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+  (void)cudaGetLastError();
   int per_sm = 0;
   e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, NT, g.smem);
   if (e != cudaSuccess || per_sm < 1) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
@@ -406,7 +433,22 @@ int launch_vp(VpArgs a, const VpGeometry& g, cudaStream_t st) {
   if (G > useful) G = (int)useful;
   if (G < a.nsub) return MDY_ERR_UNSUPPORTED;
   a.G = G;
-  kern<<<(unsigned)(G * a.nvr), NT, g.smem, st>>>(a);
+  // A cooperative launch: the runtime either makes every CTA of the grid resident at once or refuses the
+  // launch (cudaErrorCooperativeLaunchTooLarge).  The CTAs wait for one another's records, so a grid of which
+  // only a part is resident would leave the resident part waiting (bounded, but seconds) for CTAs that cannot
+  // start until it is done.
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
+  cfg.gridDim = dim3((unsigned)(G * a.nvr), 1, 1);
+  cfg.blockDim = dim3(NT, 1, 1);
+  cfg.dynamicSmemBytes = g.smem;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  e = cudaLaunchKernelEx(&cfg, kern, a);
+  if (e != cudaSuccess) { (void)cudaGetLastError(); return (int)e; }
   return finish_launch(1);
 }
 
@@ -415,6 +457,19 @@ std::mutex g_peer_mu;
 }  // namespace
 
 int ce_vp_dev_error(bool clear) { return read_dev_error(clear); }
+
+int ce_vp_dev_detail(int k, bool clear) {
+  int v[4] = {0, 0, 0, 0};
+  if (k < 0 || k > 3 || cudaMemcpyFromSymbol(v, g_vp_detail, sizeof(v)) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return -1;
+  }
+  if (clear) {
+    const int z[4] = {0, 0, 0, 0};
+    (void)cudaMemcpyToSymbol(g_vp_detail, z, sizeof(z));
+  }
+  return v[k];
+}
 
 }  // namespace mdy
 
