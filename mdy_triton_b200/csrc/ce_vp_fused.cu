@@ -373,7 +373,7 @@ __global__ void __launch_bounds__(NTC + 32) ce_vp_fused_kernel(VpArgs a) {
   }
 }
 
-struct VpGeometry { int nsub, vps, slot_bytes, nslots, lag, nt, per_sm; size_t smem; };
+struct VpGeometry { int nsub, vps, slot_bytes, nslots, lag, nt, vpc, per_sm; size_t smem; };
 
 // Slice, ring and CTA shape for shard rows of `vs` elements of `esize` bytes.
 inline bool vp_geometry(int64_t vs, int esize, int tp, VpGeometry* out) {
@@ -392,30 +392,38 @@ inline bool vp_geometry(int64_t vs, int esize, int tp, VpGeometry* out) {
   g.vps = (int)ceil_div(nvec, g.nsub);
   if ((int64_t)(g.nsub - 1) * g.vps >= nvec) return false;  // a slice would be empty
   const int64_t slice_bytes = (int64_t)g.vps * 16;
-  g.nt = slice_bytes <= 10 * 1024 ? 128 : slice_bytes <= 40 * 1024 ? 256 : 512;   // compute threads per CTA (plus one exchange warp)
-  if (ceil_div(g.vps, g.nt * 4) > kVpMaxChunks) return false;
-  // Several CTAs per SM where the slices are small, so that one CTA's barriers are covered by another's sweeps.
-  g.per_sm = g.nt == 128 ? 4 : g.nt == 256 ? 2 : 1;
+  // Compute threads per CTA (plus one exchange warp), 16-byte vectors per thread and chunk, CTAs per SM.  A row's
+  // reduction, publish and hand-offs are a serial chain of a few microseconds inside its CTA: short slices need
+  // many CTAs per SM to cover it (8 KB of logits are 0.4 us of HBM time per SM), long ones amortise it.
+  if (slice_bytes <= 8704) { g.nt = 64; g.vpc = 8; g.per_sm = 8; }
+  else if (slice_bytes <= 17408) { g.nt = 128; g.vpc = 8; g.per_sm = 4; }
+  else if (slice_bytes <= 40 * 1024) { g.nt = 256; g.vpc = 4; g.per_sm = 2; }
+  else { g.nt = 512; g.vpc = 4; g.per_sm = 1; }
+  if (ceil_div(g.vps, g.nt * g.vpc) > kVpMaxChunks) return false;
   if (tunable(MDY_TUNE_CE_VP_CTAS_PER_SM) > 0) g.per_sm = tunable(MDY_TUNE_CE_VP_CTAS_PER_SM);
   g.slot_bytes = (int)((slice_bytes + 127) / 128 * 128);
   const int fixed = kVpBarriers * 8 + (kStatsRing * 64 + kLseRing * 4) * 4 + kLabRing * 8;
-  const int budget = (227 * 1024) / g.per_sm - 1024 - fixed;
-  g.nslots = budget / g.slot_bytes;
+  // at least three slots: fewer CTAs per SM where the asked-for number leaves too little shared memory each
+  for (;; --g.per_sm) {
+    const int budget = (227 * 1024) / g.per_sm - 1024 - fixed;
+    g.nslots = budget / g.slot_bytes;
+    if (g.nslots >= 3 || g.per_sm == 1) break;
+  }
   if (g.nslots > 5) g.nslots = 5;
   if (tunable(MDY_TUNE_CE_VP_SLOTS) > 0 && tunable(MDY_TUNE_CE_VP_SLOTS) <= g.nslots) g.nslots = tunable(MDY_TUNE_CE_VP_SLOTS);
   if (g.nslots < 3) return false;
   // rows between a row's publish and its poll: what hides the exchange's latency; loads run the other
-  // two slots ahead.  At most 3: the statistics barrier has four ids.
+  // two slots ahead.  At most 3 (the hand-off rings are sized for it).
   g.lag = g.nslots - 2;
   g.smem = (size_t)g.nslots * g.slot_bytes + fixed;
   *out = g;
   return true;
 }
 
-template <typename T, int NTC>
+template <typename T, int NTC, int VPC>
 int launch_vp(VpArgs a, const VpGeometry& g, cudaStream_t st) {
   constexpr int NT = NTC + 32;
-  auto kern = ce_vp_fused_kernel<T, NTC, 4>;
+  auto kern = ce_vp_fused_kernel<T, NTC, VPC>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
   // The occupancy figure below assumes the largest shared-memory carve-out; ask for it, so that the SMs are
@@ -523,9 +531,10 @@ int mdy_ce_vp_fused(const void* const* logits, void* const* dlogits, float* cons
     VpGeometry g;
     if (!vp_geometry(shard_cols, (int)sizeof(T), tp, &g)) return (int)MDY_ERR_UNSUPPORTED;
     a.nsub = g.nsub; a.vps = g.vps; a.slot_bytes = g.slot_bytes; a.nslots = g.nslots; a.lag = g.lag;
-    if (g.nt == 128) return launch_vp<T, 128>(a, g, (cudaStream_t)stream);
-    if (g.nt == 256) return launch_vp<T, 256>(a, g, (cudaStream_t)stream);
-    return launch_vp<T, 512>(a, g, (cudaStream_t)stream);
+    if (g.nt == 64) return launch_vp<T, 64, 8>(a, g, (cudaStream_t)stream);
+    if (g.nt == 128) return launch_vp<T, 128, 8>(a, g, (cudaStream_t)stream);
+    if (g.nt == 256) return launch_vp<T, 256, 4>(a, g, (cudaStream_t)stream);
+    return launch_vp<T, 512, 4>(a, g, (cudaStream_t)stream);
   });
 }
 
