@@ -139,6 +139,30 @@ class PeerExchange:
                 self._own.value = None
 
 
+def fused_launcher(lg, lb, dlogits, inv_n, exchange: PeerExchange):
+    """Prepare repeated launches of ``mdy_ce_vp_fused`` on fixed buffers (a training loop with static shapes,
+    a benchmark): returns ``(launch, losses, lse)`` where ``launch()`` does nothing on the host but advance
+    the epoch and make the C call on the current stream of the shard's device."""
+    import ctypes
+    dev = _C.require_cuda(lg, lb, dlogits)
+    m, v = lg.shape
+    if v != exchange.shard_cols or m > exchange.max_rows or lg.dtype != exchange.dtype:
+        raise ValueError("the PeerExchange was created for another shard shape")
+    losses = torch.empty(m, dtype=torch.float32, device=dev)
+    lse = torch.empty(m, dtype=torch.float32, device=dev)
+    one = lambda t: (ctypes.c_void_p * 1)(t.data_ptr())
+    a_lg, a_dl, a_lo, a_ls = one(lg), one(dlogits), one(losses), one(lse)
+    fn = _C.lib().mdy_ce_vp_fused
+    p_lb, p_inv, stride, code = _C.ptr(lb), _C.ptr(inv_n), (lg.stride(0) if m > 1 else v), _C.dtype_code(lg)
+
+    def launch():
+        rc = fn(a_lg, a_dl, a_lo, a_ls, exchange.ptrs, p_lb, p_inv, 1.0, m, v, stride, exchange.tp, exchange.rank, 1,
+                exchange.max_rows, exchange.next_epoch(), code, torch.cuda.current_stream(dev).cuda_stream)
+        if rc != 0:
+            _C.check(rc, "mdy_ce_vp_fused")
+    return launch, losses, lse
+
+
 def fused_loss_and_grad(lg, lb, dlogits, inv_n, exchange: PeerExchange):
     """One launch of ``mdy_ce_vp_fused`` for this rank's shard ``lg`` [M, Vs]: writes ``dlogits`` (may be
     ``lg``) scaled by ``inv_n`` (float32 device scalar) and returns (losses[M], lse[M])."""
@@ -199,12 +223,12 @@ def vocab_parallel_cross_entropy(logits, labels, group=None, inplace=False):
 
 def vocab_parallel_entropy_loss(logits, labels, num_items_in_batch=None, group=None, inplace=False, exchange=None):
     """Scalar ``sum(losses) / num_items_in_batch`` on vocab-sharded logits (same on every rank).  With a
-    :class:`PeerExchange` (and gradients enabled, logits not float16) the loss and the gradient come from
-    one kernel per GPU that exchanges the row statistics through peer memory; otherwise from the
-    sweep -> all-gather -> sweep path."""
+    :class:`PeerExchange` (and gradients enabled, logits not float16, not ``inplace``: in-place callers expect
+    their logits intact until backward) the loss and the gradient come from one kernel per GPU that exchanges
+    the row statistics through peer memory; otherwise from the sweep -> all-gather -> sweep path."""
     if (exchange is not None and torch.is_grad_enabled() and logits.requires_grad
-            and logits.dtype != torch.float16):
-        return _FusedVocabParallelLoss.apply(logits, labels, num_items_in_batch, exchange, bool(inplace))
+            and logits.dtype != torch.float16 and not inplace):
+        return _FusedVocabParallelLoss.apply(logits, labels, num_items_in_batch, exchange, False)
     losses = vocab_parallel_cross_entropy(logits, labels, group, inplace)
     if num_items_in_batch is None:
         num_items_in_batch = torch.count_nonzero(labels != _ce.IGNORE_INDEX)

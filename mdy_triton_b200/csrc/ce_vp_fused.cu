@@ -20,12 +20,17 @@
 // needs no fence and no atomicity beyond that of an aligned 8-byte store.  Buffers are double-buffered by
 // epoch parity: a rank can be at most one call ahead of a peer that still reads the previous call.
 //
-// Every wait is bounded.  The poll of the exchange gives up after `wait_tries` rounds (about two
-// seconds by default): the thread then raises the device flag (mdy_last_device_error), publishes and
-// reports NaN from then on and keeps walking its rows, so the peers never wait for it and the loss
-// of the batch is NaN, not a finite wrong number.
+// Inside a CTA the work is split between compute warps, which only stream (statistics sweep of row i,
+// gradient sweep of row i - lag), and ONE exchange warp, which does everything that is latency: the end of
+// the CTA's reduction, the publish, the poll, the combine.  They hand rows to each other through mbarriers.
 //
-// The kernel assumes all its CTAs are resident at once (the grid is sized from the occupancy query) on
+// Every wait is bounded.  The poll of the exchange gives up after `wait_tries` rounds (a few seconds by
+// default), the mbarrier waits likewise: the thread then raises the device flag (mdy_last_device_error),
+// publishes and reports NaN from then on and keeps walking its rows, so the peers never wait for it and the
+// loss of the batch is NaN, not a finite wrong number.
+//
+// All CTAs of a launch have to be resident at once (they wait for one another): the grid is sized from the
+// occupancy query and launched cooperatively, so the runtime refuses it rather than run a part of it, on
 // every participating GPU; with fewer GPUs than ranks the same kernel runs all ranks as "virtual ranks" of
 // one launch (nvr > 1), which is how the protocol is tested on a single GPU.
 // No multicast copy and no remote LOAD is used: peers' memory is only ever written.
@@ -91,10 +96,6 @@ __device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
 __device__ __forceinline__ void bar_sync_id(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
-__device__ __forceinline__ void bar_arrive_id(int id, int count) {
-  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
-}
-
 // Hand-offs inside a CTA.  Between the compute warps and the exchange warp they are mbarriers, waited for
 // with the same bounded try_wait as the bulk copies, so that a slip in the protocol would show up as an
 // expired wait (flag, NaN loss), never as a hang:
@@ -114,8 +115,12 @@ constexpr int kVpBarriers = 24;   // 8-byte mbarrier slots reserved: kVpMaxSlots
 // the CTA's reduction, publishes the record to every rank, polls this rank's buffer for the records of the
 // row whose gradient comes next, combines them, and keeps the label ring filled.  The two sides meet at
 // named barriers only.
+// CTAs per SM each shape is compiled for (its register budget): one 544-thread CTA may use 120 registers a
+// thread; without the hint the compiler aimed for two and spilled.
+constexpr int vp_min_blocks(int ntc) { return ntc >= 512 ? 1 : ntc >= 256 ? 2 : ntc >= 128 ? 4 : 6; }
+
 template <typename T, int NTC, int VPC>
-__global__ void __launch_bounds__(NTC + 32) ce_vp_fused_kernel(VpArgs a) {
+__global__ void __launch_bounds__(NTC + 32, vp_min_blocks(NTC)) ce_vp_fused_kernel(VpArgs a) {
   constexpr int VE = VecInfo<T>::kElems;
   constexpr int CV = NTC * VPC;  // vectors per chunk
   constexpr int NWC = NTC / 32;  // compute warps
@@ -399,6 +404,13 @@ inline bool vp_geometry(int64_t vs, int esize, int tp, VpGeometry* out) {
   else if (slice_bytes <= 17408) { g.nt = 128; g.vpc = 8; g.per_sm = 4; }
   else if (slice_bytes <= 40 * 1024) { g.nt = 256; g.vpc = 4; g.per_sm = 2; }
   else { g.nt = 512; g.vpc = 4; g.per_sm = 1; }
+  // 16-bit logits: a slice of between four and six vectors per thread is swept as ONE chunk of six instead of a
+  // full chunk of four and a mostly empty second one (19 KB slices: 0.61 against 0.55 of the copy bandwidth).
+  // Eight per thread in one chunk measured slower than two chunks of four (32 KB slices: 0.72 against 0.75).
+  if (esize == 2 && g.nt >= 256) {
+    const int64_t need = ceil_div(g.vps, g.nt);
+    if (need > 4 && need <= 6) g.vpc = 6;
+  }
   if (ceil_div(g.vps, g.nt * g.vpc) > kVpMaxChunks) return false;
   if (tunable(MDY_TUNE_CE_VP_CTAS_PER_SM) > 0) g.per_sm = tunable(MDY_TUNE_CE_VP_CTAS_PER_SM);
   g.slot_bytes = (int)((slice_bytes + 127) / 128 * 128);
@@ -533,6 +545,10 @@ int mdy_ce_vp_fused(const void* const* logits, void* const* dlogits, float* cons
     a.nsub = g.nsub; a.vps = g.vps; a.slot_bytes = g.slot_bytes; a.nslots = g.nslots; a.lag = g.lag;
     if (g.nt == 64) return launch_vp<T, 64, 8>(a, g, (cudaStream_t)stream);
     if (g.nt == 128) return launch_vp<T, 128, 8>(a, g, (cudaStream_t)stream);
+    if constexpr (sizeof(T) == 2) {
+      if (g.nt == 256 && g.vpc == 6) return launch_vp<T, 256, 6>(a, g, (cudaStream_t)stream);
+      if (g.nt == 512 && g.vpc == 6) return launch_vp<T, 512, 6>(a, g, (cudaStream_t)stream);
+    }
     if (g.nt == 256) return launch_vp<T, 256, 4>(a, g, (cudaStream_t)stream);
     return launch_vp<T, 512, 4>(a, g, (cudaStream_t)stream);
   });
