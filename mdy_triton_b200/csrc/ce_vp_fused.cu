@@ -404,12 +404,17 @@ inline bool vp_geometry(int64_t vs, int esize, int tp, VpGeometry* out) {
   else if (slice_bytes <= 17408) { g.nt = 128; g.vpc = 8; g.per_sm = 4; }
   else if (slice_bytes <= 40 * 1024) { g.nt = 256; g.vpc = 4; g.per_sm = 2; }
   else { g.nt = 512; g.vpc = 4; g.per_sm = 1; }
-  // 16-bit logits: a slice of between four and six vectors per thread is swept as ONE chunk of six instead of a
-  // full chunk of four and a mostly empty second one (19 KB slices: 0.61 against 0.55 of the copy bandwidth).
+  // 16-bit logits: the chunk width (4, 5 or 6 vectors per thread) that leaves the fewest empty lanes in the last
+  // chunk.  A 19 KB slice is swept as one chunk of five or six instead of a full chunk of four and a mostly empty
+  // second one (0.61 against 0.55 of the copy bandwidth), a 37 KB slice as two of five instead of three of four.
   // Eight per thread in one chunk measured slower than two chunks of four (32 KB slices: 0.72 against 0.75).
   if (esize == 2 && g.nt >= 256) {
     const int64_t need = ceil_div(g.vps, g.nt);
-    if (need > 4 && need <= 6) g.vpc = 6;
+    int64_t best = ceil_div(need, 4) * 4;
+    for (int c = 5; c <= 6; ++c) {
+      const int64_t padded = ceil_div(need, c) * c;
+      if (padded < best) { best = padded; g.vpc = c; }
+    }
   }
   if (ceil_div(g.vps, g.nt * g.vpc) > kVpMaxChunks) return false;
   if (tunable(MDY_TUNE_CE_VP_CTAS_PER_SM) > 0) g.per_sm = tunable(MDY_TUNE_CE_VP_CTAS_PER_SM);
@@ -546,6 +551,8 @@ int mdy_ce_vp_fused(const void* const* logits, void* const* dlogits, float* cons
     if (g.nt == 64) return launch_vp<T, 64, 8>(a, g, (cudaStream_t)stream);
     if (g.nt == 128) return launch_vp<T, 128, 8>(a, g, (cudaStream_t)stream);
     if constexpr (sizeof(T) == 2) {
+      if (g.nt == 256 && g.vpc == 5) return launch_vp<T, 256, 5>(a, g, (cudaStream_t)stream);
+      if (g.nt == 512 && g.vpc == 5) return launch_vp<T, 512, 5>(a, g, (cudaStream_t)stream);
       if (g.nt == 256 && g.vpc == 6) return launch_vp<T, 256, 6>(a, g, (cudaStream_t)stream);
       if (g.nt == 512 && g.vpc == 6) return launch_vp<T, 512, 6>(a, g, (cudaStream_t)stream);
     }

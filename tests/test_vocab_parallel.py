@@ -344,5 +344,17 @@ def test_peer_exchange_object_and_fused_loss_single_rank():
             lb_ = core.triton_entropy_loss(b, lb); lb_.backward()
             assert abs(float(la) - float(lb_)) <= LOSS_TOL * max(1.0, abs(float(lb_)))
             assert_close(a.grad, b.grad, 1e-2, "gradient")
+        # the prepared launcher (fixed buffers, nothing but the C call per step), in place, twice
+        n = (lb != -100).sum().float()
+        inv = (1.0 / n).reshape(1)
+        work = lg.clone()
+        launch, losses, _ = vp.fused_launcher(work, lb, work, inv, ex)
+        for _ in range(2):
+            work.copy_(lg)
+            launch()
+            assert abs(float(losses.sum() / n) - float(lb_)) <= LOSS_TOL * max(1.0, abs(float(lb_)))
+            assert_close(work, b.grad, 1e-2, "gradient from the prepared launcher")
+        from mdy_triton_b200 import _C
+        assert _C.lib().mdy_last_device_error(1) == 0
     finally:
         ex.close()
