@@ -655,14 +655,15 @@ def run_vpce(dev, dist, world, rank, steps, warmup, check=True):
                 err = (work2.float() - want).abs()
                 grad_ok = bool((err <= 1e-2 * (want.abs() + want.abs().mean())).all())
                 del work2, want, err
-                case["full_vocab_loss"] = float(ref)
-                ok = abs(loss - float(ref)) <= 1e-4 * max(1.0, abs(float(ref))) and grad_ok
+                ref = float(ref.detach())
+                case["full_vocab_loss"] = ref
+                ok = abs(loss - ref) <= 1e-4 * max(1.0, abs(ref)) and grad_ok
                 if dist is not None:
                     flag = torch.tensor([0 if ok else 1], device=dev)
                     dist.all_reduce(flag)
                     ok = int(flag[0]) == 0
                 if not ok:
-                    parity = f"MISMATCH at vocab {V} sigma {sigma}: {loss} vs {float(ref)}, gradient ok: {grad_ok}"
+                    parity = f"MISMATCH at vocab {V} sigma {sigma}: {loss} vs {ref}, gradient ok: {grad_ok}"
                 del full, ref
             cases.append(case)
             if exchange is not None:

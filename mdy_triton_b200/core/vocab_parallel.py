@@ -121,7 +121,8 @@ class PeerExchange:
         self.ptrs = (ctypes.c_void_p * self.tp)(*ptrs)
 
     def next_epoch(self):
-        self.epoch = self.epoch + 1 if self.epoch < 0xFFFFFFFF else 1
+        # wraps from the odd 0xFFFFFFFF to the even 2: consecutive launches always use different halves of the buffers
+        self.epoch = self.epoch + 1 if self.epoch < 0xFFFFFFFF else 2
         return self.epoch
 
     def close(self):
