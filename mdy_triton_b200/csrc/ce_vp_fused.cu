@@ -119,7 +119,11 @@ constexpr int kVpBarriers = 24;   // 8-byte mbarrier slots reserved: kVpMaxSlots
 // thread; without the hint the compiler aimed for two and spilled.
 constexpr int vp_min_blocks(int ntc) { return ntc >= 512 ? 1 : ntc >= 256 ? 2 : ntc >= 128 ? 4 : 6; }
 
-template <typename T, int NTC, int VPC>
+// PV: the last, partial chunk of the statistics sweep is swept one vector at a time, so that a thread does only
+// the vectors it really has.  It costs registers (1-2 % on shapes whose last chunk is nearly full) and wins 5 %
+// where a whole vector per thread would be empty (seven vectors per thread in two chunks of four), so it is a
+// compile-time variant the launcher picks by the slice length.
+template <typename T, int NTC, int VPC, bool PV>
 __global__ void __launch_bounds__(NTC + 32, vp_min_blocks(NTC)) ce_vp_fused_kernel(VpArgs a) {
   constexpr int VE = VecInfo<T>::kElems;
   constexpr int CV = NTC * VPC;  // vectors per chunk
@@ -290,13 +294,22 @@ __global__ void __launch_bounds__(NTC + 32, vp_min_blocks(NTC)) ce_vp_fused_kern
             stats_chunk<T, VPC>(q, m, s0, s1);
           }
           if (nfull < nchunk) {
-            uint4 q[VPC];
+            if constexpr (PV) {
+#pragma unroll 1
+              for (int vb = nfull * CV; vb + ct < my_nvec; vb += NTC) {
+                uint4 q[1];
+                q[0] = lds128(base + (uint32_t)vb * 16u);
+                stats_chunk<T, 1>(q, m, s0, s1);
+              }
+            } else {
+              uint4 q[VPC];
 #pragma unroll
-            for (int jv = 0; jv < VPC; ++jv) {
-              const int vb = nfull * CV + jv * NTC;
-              q[jv] = vb + ct < my_nvec ? lds128(base + (uint32_t)vb * 16u) : neg_inf_vec<T>();
+              for (int jv = 0; jv < VPC; ++jv) {
+                const int vb = nfull * CV + jv * NTC;
+                q[jv] = vb + ct < my_nvec ? lds128(base + (uint32_t)vb * 16u) : neg_inf_vec<T>();
+              }
+              stats_chunk<T, VPC>(q, m, s0, s1);
             }
-            stats_chunk<T, VPC>(q, m, s0, s1);
           }
         }
         float s = s0 + s1;
@@ -437,10 +450,10 @@ inline bool vp_geometry(int64_t vs, int esize, int tp, VpGeometry* out) {
   return true;
 }
 
-template <typename T, int NTC, int VPC>
+template <typename T, int NTC, int VPC, bool PV = false>
 int launch_vp(VpArgs a, const VpGeometry& g, cudaStream_t st) {
   constexpr int NT = NTC + 32;
-  auto kern = ce_vp_fused_kernel<T, NTC, VPC>;
+  auto kern = ce_vp_fused_kernel<T, NTC, VPC, PV>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
   // The occupancy figure below assumes the largest shared-memory carve-out; ask for it, so that the SMs are
@@ -548,6 +561,15 @@ int mdy_ce_vp_fused(const void* const* logits, void* const* dlogits, float* cons
     VpGeometry g;
     if (!vp_geometry(shard_cols, (int)sizeof(T), tp, &g)) return (int)MDY_ERR_UNSUPPORTED;
     a.nsub = g.nsub; a.vps = g.vps; a.slot_bytes = g.slot_bytes; a.nslots = g.nslots; a.lag = g.lag;
+    // a whole vector per thread (or more) of the last chunk is empty: sweep that chunk vector by vector
+    const int64_t need = ceil_div(g.vps, g.nt);
+    const bool pv = ceil_div(need, g.vpc) * g.vpc > need;
+    if (pv) {
+      if (g.nt == 64) return launch_vp<T, 64, 8, true>(a, g, (cudaStream_t)stream);
+      if (g.nt == 128) return launch_vp<T, 128, 8, true>(a, g, (cudaStream_t)stream);
+      if (g.nt == 256 && g.vpc == 4) return launch_vp<T, 256, 4, true>(a, g, (cudaStream_t)stream);
+      if (g.nt == 512 && g.vpc == 4) return launch_vp<T, 512, 4, true>(a, g, (cudaStream_t)stream);
+    }
     if (g.nt == 64) return launch_vp<T, 64, 8>(a, g, (cudaStream_t)stream);
     if (g.nt == 128) return launch_vp<T, 128, 8>(a, g, (cudaStream_t)stream);
     if constexpr (sizeof(T) == 2) {
