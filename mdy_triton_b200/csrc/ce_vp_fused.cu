@@ -17,7 +17,7 @@
 // A shard row longer than a slot is cut into `nsub` column slices handled by different CTAs; they are
 // participants of the exchange like the peers' CTAs (through this GPU's own buffer), so a row has
 // P = ranks * nsub participants.  Each 8-byte half of a record carries its own epoch tag, so the record
-// needs no fence and no atomicity beyond that of an aligned 8-byte store.  Buffers are double-buffered by
+// needs no fence and no atomicity beyond that of an aligned 64-bit vector element.  Buffers are double-buffered by
 // epoch parity: a rank can be at most one call ahead of a peer that still reads the previous call.
 //
 // Inside a CTA the work is split between compute warps, which only stream (statistics sweep of row i,
@@ -84,13 +84,16 @@ __device__ __forceinline__ void vp_wait(int kind, int i, uint32_t bar, uint32_t 
   if (!was && dead) note_expiry(kind, i);
 }
 
+// A record is two 64-bit words {value, tag}: written and read as vectors of 64-bit ELEMENTS, the unit the memory
+// model keeps whole in a vector access, so a word is never seen with a new tag and an old value.
 __device__ __forceinline__ void st_volatile_v4(uint4* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+  const unsigned long long lo = ((unsigned long long)b << 32) | a, hi = ((unsigned long long)d << 32) | c;
+  asm volatile("st.volatile.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(lo), "l"(hi) : "memory");
 }
 __device__ __forceinline__ uint4 ld_volatile_v4(const uint4* p) {
-  uint4 v;
-  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-  return v;
+  unsigned long long lo, hi;
+  asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "l"(p) : "memory");
+  return make_uint4((uint32_t)lo, (uint32_t)(lo >> 32), (uint32_t)hi, (uint32_t)(hi >> 32));
 }
 
 __device__ __forceinline__ void bar_sync_id(int id, int count) {
