@@ -247,9 +247,9 @@ def _fused_all_ranks_one_gpu(lib, shards, outs, labels, inv_n, xbufs, xrows, epo
     (32000, 4, 2.0, torch.float16, 64),
 ])
 def test_one_kernel_exchange_all_ranks_on_one_gpu(v, tp, sigma, dt, m):
-    """mdy_ce_vp_fused against the full-vocabulary oracle: losses, lse and every rank's gradient columns, on two
-    calls in a row with different logits (the exchange buffers keep the previous call's records, told apart by
-    the epoch), the second one in place."""
+    """mdy_ce_vp_fused against the full-vocabulary oracle: losses, lse and every rank's gradient columns, on three
+    calls in a row with different logits (the exchange buffers keep earlier calls' records, told apart by the
+    epoch; the third call finds the first call's records in its half of the buffers), the second one in place."""
     from mdy_triton_b200 import _C
     lib = _C.lib()
     dev = torch.device("cuda", 0)
@@ -260,7 +260,7 @@ def test_one_kernel_exchange_all_ranks_on_one_gpu(v, tp, sigma, dt, m):
     xbufs = [torch.zeros(nbytes, dtype=torch.uint8, device=dev) for _ in range(tp)]
     rel = 1e-2 if dt != torch.float32 else 1e-4
     atol = 2.0 ** -24 if dt == torch.float16 else 0.0
-    for call, inplace in ((1, False), (2, True)):
+    for call, inplace in ((1, False), (2, True), (3, False)):
         g = torch.Generator().manual_seed(100 * call + tp)
         lg = (torch.randn(m, v, generator=g) * sigma).to(dt)
         lb = torch.randint(0, v, (m,), generator=g); lb[torch.rand(m, generator=g) < 0.05] = -100
