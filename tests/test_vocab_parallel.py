@@ -175,20 +175,23 @@ def _nccl_worker(rank, world, port, out):
         g = shard.grad.float().cpu()
         ok = torch.allclose(losses.cpu(), fl, rtol=1e-4, atol=1e-4) and bool(((g - full).abs() <= 1e-2 * (full.abs() + full.abs().mean())).all())
         # the one-kernel path: records stored straight into the peer's exchange buffer (mapped through CUDA IPC),
-        # two calls in a row on the same buffers
+        # four calls in a row on the same buffers, each with other logits: a record left over from two calls
+        # earlier (same half of the buffers) would give a wrong loss
         from mdy_triton_b200.core.vocab_parallel import PeerExchange, vocab_parallel_entropy_loss
         from mdy_triton_b200 import _C
         ex = PeerExchange(lg.shape[0], v, torch.bfloat16, dev)
         try:
             n = int((lb != -100).sum())
-            want = E.ce_grad(lg, lb, fs, torch.tensor(1.0 / n))[:, rank * v:(rank + 1) * v]
-            for _ in range(2):
-                leaf = lg[:, rank * v:(rank + 1) * v].contiguous().to(dev).requires_grad_(True)
+            for call in range(4):
+                lgc = (lg.float() * (1.0 + 0.25 * call)).to(torch.bfloat16)
+                flc, fsc = E.ce_rows(lgc, lb)
+                want = E.ce_grad(lgc, lb, fsc, torch.tensor(1.0 / n))[:, rank * v:(rank + 1) * v]
+                leaf = lgc[:, rank * v:(rank + 1) * v].contiguous().to(dev).requires_grad_(True)
                 loss = vocab_parallel_entropy_loss(leaf, lb.to(dev), exchange=ex)
                 loss.backward()
                 torch.cuda.synchronize()
                 g2 = leaf.grad.float().cpu()
-                ok = (ok and abs(float(loss) - float(fl.sum() / n)) <= 1e-4 * max(1.0, float(fl.sum() / n))
+                ok = (ok and abs(float(loss) - float(flc.sum() / n)) <= 1e-4 * max(1.0, float(flc.sum() / n))
                       and bool(((g2 - want).abs() <= 1e-2 * (want.abs() + want.abs().mean())).all())
                       and _C.lib().mdy_last_device_error(1) == 0)
         finally:
