@@ -120,7 +120,7 @@ constexpr int kVpBarriers = 24;   // 8-byte mbarrier slots reserved: kVpMaxSlots
 // named barriers only.
 // CTAs per SM each shape is compiled for (its register budget): one 544-thread CTA may use 120 registers a
 // thread; without the hint the compiler aimed for two and spilled.
-constexpr int vp_min_blocks(int ntc) { return ntc >= 512 ? 1 : ntc >= 256 ? 2 : ntc >= 128 ? 4 : 6; }
+constexpr int vp_min_blocks(int ntc) { return ntc >= 512 ? 1 : ntc >= 256 ? 2 : ntc >= 128 ? 4 : 8; }
 
 // PV: the last, partial chunk of the statistics sweep is swept one vector at a time, so that a thread does only
 // the vectors it really has.  It costs registers (1-2 % on shapes whose last chunk is nearly full) and wins 5 %
