@@ -126,8 +126,8 @@ constexpr int vp_min_blocks(int ntc) { return ntc >= 512 ? 1 : ntc >= 256 ? 2 : 
 // the vectors it really has.  It costs registers (1-2 % on shapes whose last chunk is nearly full) and wins 5 %
 // where a whole vector per thread would be empty (seven vectors per thread in two chunks of four), so it is a
 // compile-time variant the launcher picks by the slice length.
-template <typename T, int NTC, int VPC, bool PV>
-__global__ void __launch_bounds__(NTC + 32, vp_min_blocks(NTC)) ce_vp_fused_kernel(VpArgs a) {
+template <typename T, int NTC, int VPC, bool PV, int MINB = vp_min_blocks(NTC)>
+__global__ void __launch_bounds__(NTC + 32, MINB) ce_vp_fused_kernel(VpArgs a) {
   constexpr int VE = VecInfo<T>::kElems;
   constexpr int CV = NTC * VPC;  // vectors per chunk
   constexpr int NWC = NTC / 32;  // compute warps
@@ -431,6 +431,9 @@ inline bool vp_geometry(int64_t vs, int esize, int tp, VpGeometry* out) {
       const int64_t padded = ceil_div(need, c) * c;
       if (padded < best) { best = padded; g.vpc = c; }
     }
+    // a slice swept as ONE chunk of five or six and short enough for three slots in a third of the shared memory:
+    // three CTAs per SM (27 warps instead of 18; the kernel is compiled for 72 registers there)
+    if (g.nt == 256 && need <= g.vpc && slice_bytes <= 23 * 1024) g.per_sm = 3;
   }
   if (ceil_div(g.vps, g.nt * g.vpc) > kVpMaxChunks) return false;
   if (tunable(MDY_TUNE_CE_VP_CTAS_PER_SM) > 0) g.per_sm = tunable(MDY_TUNE_CE_VP_CTAS_PER_SM);
@@ -453,10 +456,10 @@ inline bool vp_geometry(int64_t vs, int esize, int tp, VpGeometry* out) {
   return true;
 }
 
-template <typename T, int NTC, int VPC, bool PV = false>
+template <typename T, int NTC, int VPC, bool PV = false, int MINB = vp_min_blocks(NTC)>
 int launch_vp(VpArgs a, const VpGeometry& g, cudaStream_t st) {
   constexpr int NT = NTC + 32;
-  auto kern = ce_vp_fused_kernel<T, NTC, VPC, PV>;
+  auto kern = ce_vp_fused_kernel<T, NTC, VPC, PV, MINB>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)g.smem);
   if (e != cudaSuccess) { (void)cudaGetLastError(); return MDY_ERR_UNSUPPORTED; }
   // The occupancy figure below assumes the largest shared-memory carve-out; ask for it, so that the SMs are
@@ -576,6 +579,8 @@ int mdy_ce_vp_fused(const void* const* logits, void* const* dlogits, float* cons
     if (g.nt == 64) return launch_vp<T, 64, 8>(a, g, (cudaStream_t)stream);
     if (g.nt == 128) return launch_vp<T, 128, 8>(a, g, (cudaStream_t)stream);
     if constexpr (sizeof(T) == 2) {
+      if (g.nt == 256 && g.per_sm == 3 && g.vpc == 5) return launch_vp<T, 256, 5, false, 3>(a, g, (cudaStream_t)stream);
+      if (g.nt == 256 && g.per_sm == 3 && g.vpc == 6) return launch_vp<T, 256, 6, false, 3>(a, g, (cudaStream_t)stream);
       if (g.nt == 256 && g.vpc == 5) return launch_vp<T, 256, 5>(a, g, (cudaStream_t)stream);
       if (g.nt == 512 && g.vpc == 5) return launch_vp<T, 512, 5>(a, g, (cudaStream_t)stream);
       if (g.nt == 256 && g.vpc == 6) return launch_vp<T, 256, 6>(a, g, (cudaStream_t)stream);
