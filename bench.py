@@ -684,7 +684,7 @@ def run_vpce(dev, dist, world, rank, steps, warmup, check=True):
                 err = (work2.float() - want).abs()
                 tol = 1e-2 * (want.abs() + want.abs().mean())
                 grad_ok = bool((err <= tol).all())
-                if not grad_ok:   # say on stderr where, the JSON line only carries the verdict
+                if not grad_ok:   # say on stderr where; the JSON line only says ok or not
                     over = err > tol
                     rows_off = over.any(dim=1).nonzero().flatten()
                     print(f"[vpce check] rank {rank} vocab {V} sigma {sigma}: {int(over.sum())} gradient elements off in "
