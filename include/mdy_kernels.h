@@ -279,6 +279,12 @@ int mdy_ce_vp_fused(const void* const* logits, void* const* dlogits, float* cons
                     void* stream);
 /* Bytes of one rank's exchange buffer for up to max_rows rows (negative: MDY_ERR_*). */
 int64_t mdy_ce_vp_exchange_bytes(int64_t max_rows, int64_t shard_cols, int tp, int dtype);
+/* The launch shape mdy_ce_vp_fused picks for shards of shard_cols columns over tp ranks (host arithmetic only, no
+ * device needed; no counterpart in the reference): out8 = {column slices per shard row, 16-byte vectors per
+ * slice, bytes of a shared-memory slot, slots per CTA, rows between a row's publish and its poll, compute
+ * threads per CTA, vectors per thread and chunk, CTAs per SM asked for}.  MDY_ERR_UNSUPPORTED where
+ * mdy_ce_vp_fused would return it for the shape. */
+int mdy_ce_vp_geometry(int64_t shard_cols, int tp, int dtype, int32_t* out8);
 
 /* Set-up of memory that peers write into (not on the hot path; the reference has no counterpart: it
  * leaves the exchange to NCCL).  create: cudaMalloc + zero fill on the current device, and the 64-byte

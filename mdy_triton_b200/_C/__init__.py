@@ -74,6 +74,7 @@ SIGNATURES = {
     "mdy_ce_vp_combine": (_I, [_P, _P, _P, _P, _L, _L, _P]),
     "mdy_ce_vp_fused": (_I, [_P, _P, _P, _P, _P, _P, _P, _F, _L, _L, _L, _I, _I, _I, _L, ctypes.c_uint32, _I, _P]),
     "mdy_ce_vp_exchange_bytes": (_L, [_L, _L, _I, _I]),
+    "mdy_ce_vp_geometry": (_I, [_L, _I, _I, _P]),
     "mdy_peer_buffer_create": (_I, [_L, _P, _P]),
     "mdy_peer_buffer_open": (_I, [_P, _P]),
     "mdy_peer_buffer_close": (_I, [_P]),

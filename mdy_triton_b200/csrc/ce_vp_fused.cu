@@ -530,6 +530,18 @@ int64_t mdy_ce_vp_exchange_bytes(int64_t max_rows, int64_t shard_cols, int tp, i
   return (int64_t)2 * max_rows * tp * g.nsub * 16;
 }
 
+int mdy_ce_vp_geometry(int64_t shard_cols, int tp, int dtype, int32_t* out8) {
+  if (!out8) return MDY_ERR_NULL;
+  if (shard_cols <= 0 || tp <= 0 || tp > kVpMaxRanks) return MDY_ERR_SIZE;
+  const int esize = dtype == MDY_F32 ? 4 : (dtype == MDY_F16 || dtype == MDY_BF16) ? 2 : 0;
+  if (!esize) return MDY_ERR_DTYPE;
+  VpGeometry g;
+  if (!vp_geometry(shard_cols, esize, tp, &g)) return MDY_ERR_UNSUPPORTED;
+  const int v[8] = {g.nsub, g.vps, g.slot_bytes, g.nslots, g.lag, g.nt, g.vpc, g.per_sm};
+  for (int k = 0; k < 8; ++k) out8[k] = v[k];
+  return MDY_OK;
+}
+
 int mdy_ce_vp_fused(const void* const* logits, void* const* dlogits, float* const* losses, float* const* lse,
                     void* const* exchange, const int64_t* labels, const float* grad_scale_dev,
                     float grad_scale_host, int64_t M, int64_t shard_cols, int64_t row_stride, int tp,

@@ -361,3 +361,43 @@ def test_peer_exchange_object_and_fused_loss_single_rank():
         assert _C.lib().mdy_last_device_error(1) == 0
     finally:
         ex.close()
+
+
+@pytest.mark.parametrize("v,tp,want", [
+    # vocabulary, ranks -> (column slices per shard row, compute threads, vectors per thread and chunk, CTAs per SM)
+    (32000, 8, (1, 64, 8, 8)),       # 8 KB rows: small CTAs, eight per SM
+    (32000, 4, (1, 128, 8, 4)),
+    (128256, 8, (1, 256, 4, 2)),     # 32 KB slices
+    (128256, 1, (4, 512, 4, 1)),     # 250 KB rows: four 64 KB slices
+    (151936, 8, (2, 256, 5, 3)),     # two 19 KB slices, one chunk of five, three CTAs per SM
+    (256000, 8, (2, 256, 4, 2)),
+])
+def test_one_kernel_launch_shape_by_shard_length(v, tp, want):
+    """The launch shape of mdy_ce_vp_fused is host arithmetic (mdy_ce_vp_geometry): pin the shapes the measured
+    configurations run with, and the invariants the kernel relies on, without a GPU."""
+    import ctypes
+    from mdy_triton_b200 import _C
+    lib = _C.lib()
+    out = (ctypes.c_int32 * 8)()
+    assert lib.mdy_ce_vp_geometry(v // tp, tp, _C.MDY_BF16, out) == 0
+    nsub, vps, slot_bytes, nslots, lag, nt, vpc, per_sm = list(out)
+    assert (nsub, nt, vpc, per_sm) == want
+    assert nsub * tp <= 32                                  # participants of a row: one lane of the exchange warp each
+    assert nsub * vps * 8 >= v // tp > (nsub - 1) * vps * 8  # the slices cover the shard row, none is empty
+    assert slot_bytes % 128 == 0 and slot_bytes >= vps * 16
+    assert 3 <= nslots <= 5 and lag == nslots - 2
+    assert per_sm * (nslots * slot_bytes + 4096) <= 227 * 1024
+    assert lib.mdy_ce_vp_exchange_bytes(16384, v // tp, tp, _C.MDY_BF16) == 2 * 16384 * tp * nsub * 16
+
+
+def test_one_kernel_launch_shape_rejects_what_the_kernel_rejects():
+    import ctypes
+    from mdy_triton_b200 import _C
+    lib = _C.lib()
+    out = (ctypes.c_int32 * 8)()
+    # status codes of include/mdy_kernels.h: -1 null pointer, -2 dtype, -3 size, -4 unsupported
+    assert lib.mdy_ce_vp_geometry(4001, 8, _C.MDY_BF16, out) == -4    # not whole 16-byte vectors
+    assert lib.mdy_ce_vp_geometry(1 << 20, 8, _C.MDY_BF16, out) == -4  # more than 32 participants
+    assert lib.mdy_ce_vp_geometry(4000, 0, _C.MDY_BF16, out) == -3
+    assert lib.mdy_ce_vp_geometry(4000, 8, 7, out) == -2
+    assert lib.mdy_ce_vp_geometry(4000, 8, _C.MDY_BF16, None) == -1
